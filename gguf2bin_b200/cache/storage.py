@@ -12,6 +12,9 @@ every group has storage of its own:
   With ``planes == 1`` a page holds ONE panel per kv head, which a mixer reads both as keys
   and as values (latents from which keys and values are projected): ``[layers, pages, 1,
   kv_heads, page_size, head_dim]``.
+  With ``rows`` a panel has that many rows instead of one per token: what a mixer keeps per
+  BLOCK of positions (means of keys and values, say) lives in the page where the block starts,
+  so it comes and goes with the sequence's pages and costs ``rows / page_size`` of their memory.
 * ``StateNeed``: a fixed-size state per sequence (for mixers that carry a state instead
   of keys).  Storage ``[layers, slots, *shape]``, cleared when a slot is opened.
   ``by_position``: the state is a ring whose places are indexed by token position, deep
@@ -55,10 +58,13 @@ class KVNeed:
     head_dim: int
     window: int = 0          # 0: every position is kept
     planes: int = 2          # 2: keys and values; 1: one panel per kv head that is both
+    rows: int = 0            # rows a page holds per panel; 0: one per token of the page
 
     @property
     def group_key(self):
         key = ("kv", self.n_kv_heads, self.head_dim, "window" if self.window else "full")
+        if self.rows:
+            key = key + (f"{self.rows} rows",)
         return key if self.planes == 2 else key + (f"{self.planes} plane",)
 
 
@@ -122,7 +128,7 @@ class Cache:
             need, nl = g["need"], len(g["layers"])
             if isinstance(need, KVNeed):
                 g["storage"] = torch.zeros(
-                    (nl, n_pages + 1, need.planes, need.n_kv_heads, self.page_size, need.head_dim),
+                    (nl, n_pages + 1, need.planes, need.n_kv_heads, need.rows or self.page_size, need.head_dim),
                     dtype=dtype, device=self.device)
             else:
                 g["storage"] = torch.zeros((nl, n_slots + 1) + tuple(need.shape), dtype=need.dtype,

@@ -20,6 +20,13 @@
 // `q_stride`: elements between the query rows of two tokens (the queries may be columns of a wider
 // product's output).  `gate` (one number per token and head, or null): the head's output is
 // multiplied by its sigmoid.
+//
+// `pool` > 0 (with a window): in front of the window's keys a token also sees one key and value for
+// every block of `pool` positions that lies wholly before the window, block b if
+// b pool + pool - 1 <= pos - window; they come from a second store (`pooled`, [pages, 2, nkv,
+// pool_rows, hd]; block b in the page of its first position at row b - ceil(that page's first
+// position / pool)) and share the softmax with the window's keys.  Blocks are visited first, in
+// chunks of 32 from block 0, so the order still depends on the token's position only.
 #include "common.cuh"
 
 G2B_DEFINE_LAST_ERROR
@@ -34,7 +41,8 @@ attn_generic_kernel(const T *__restrict__ q, T *__restrict__ out, const T *__res
                     const int *__restrict__ page_table, int P, int n_tokens, int nh, int nkv,
                     int hd, int page_size, int window, float scale,
                     const float *__restrict__ sink, int planes, int q_stride,
-                    const T *__restrict__ gate, int gate_stride, int chunk) {
+                    const T *__restrict__ gate, int gate_stride, int chunk, const T *__restrict__ pooled,
+                    int pool, int pool_rows) {
   pdl_launch();
   pdl_wait();
   __shared__ float qs[AG_WARPS][AG_MAX_HD];
@@ -56,6 +64,46 @@ attn_generic_kernel(const T *__restrict__ q, T *__restrict__ out, const T *__res
   for (int i = 0; i < AG_MAX_HD / 32; ++i) acc[i] = 0.f;
 
   const size_t head_stride = (size_t)page_size * hd;              // one (page, K|V, kv head) panel
+  if (pool > 0) {
+    const int n_blocks = max(0, (pos - window + 1) / pool);       // window > 0 (the launcher checks)
+    const size_t pstride = (size_t)pool_rows * hd;
+    auto row_of = [&](int blk, const T *&kr, const T *&vr) {
+      const int home = (blk * pool) / page_size;
+      const int row = blk - (home * page_size + pool - 1) / pool;
+      const size_t page = (size_t)page_table[(size_t)b * P + home];
+      kr = pooled + ((page * 2 + 0) * nkv + kvh) * pstride + (size_t)row * hd;
+      vr = pooled + ((page * 2 + 1) * nkv + kvh) * pstride + (size_t)row * hd;
+    };
+    for (int base = 0; base < n_blocks; base += 32) {
+      const bool valid = base + lane < n_blocks;
+      float s = -INFINITY;
+      if (valid) {
+        const T *kr, *vr;
+        row_of(base + lane, kr, vr);
+        float dot = 0.f;
+        for (int j = 0; j < hd; ++j) dot = fmaf(qs[warp][j], to_f32(kr[j]), dot);
+        s = dot * scale;
+      }
+      const float m_new = fmaxf(m, warp_max(s));                  // finite: block `base` is valid
+      const float p = valid ? expf(s - m_new) : 0.f;
+      const float corr = expf(m - m_new);
+      l = l * corr + warp_sum(p);
+#pragma unroll
+      for (int i = 0; i < AG_MAX_HD / 32; ++i) acc[i] *= corr;
+      const int n_here = min(32, n_blocks - base);
+      for (int j = 0; j < n_here; ++j) {
+        const float pj = __shfl_sync(0xffffffffu, p, j);
+        const T *kr, *vr;
+        row_of(base + j, kr, vr);
+#pragma unroll
+        for (int i = 0; i < AG_MAX_HD / 32; ++i) {
+          const int d = lane + 32 * i;
+          if (d < hd) acc[i] = fmaf(pj, to_f32(vr[d]), acc[i]);
+        }
+      }
+      m = m_new;
+    }
+  }
   for (int base = (lo / 32) * 32; base <= pos; base += 32) {
     const int page = page_table[(size_t)b * P + base / page_size];
     const T *kpanel = cache + (((size_t)page * planes + 0) * nkv + kvh) * head_stride;
@@ -104,8 +152,12 @@ extern "C" int g2b_attn_generic(const void *q, void *out, int dtype, const void 
                                 const int *tok_pos, const int *tok_seq, const int *page_table,
                                 int P, int n_tokens, int nh, int nkv, int hd, int page_size,
                                 int window, float scale, const float *sink, int planes, int q_stride,
-                                const void *gate, int gate_stride, int chunk, cudaStream_t stream) {
+                                const void *gate, int gate_stride, int chunk, const void *pooled, int pool,
+                                int pool_rows, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
+  if (pool < 0 || (pool > 0 && (window <= 0 || !pooled || planes != 2 || pool_rows < (page_size + pool - 1) / pool)))
+    G2B_REFUSE("attn_generic: pooled blocks of %d need a window, their store and %d rows a page", pool,
+               pool > 0 ? (page_size + pool - 1) / pool : 0);
   if (chunk < 0 || (chunk > 0 && window > 0)) G2B_REFUSE("attn_generic: a chunk of %d keys with a window of %d", chunk, window);
   if (planes != 1 && planes != 2) G2B_REFUSE("attn_generic: %d panels per page and kv head (1 or 2)", planes);
   if (hd <= 0 || hd > AG_MAX_HD) G2B_REFUSE("attn_generic: head_dim %d outside 1..%d", hd, AG_MAX_HD);
@@ -117,11 +169,11 @@ extern "C" int g2b_attn_generic(const void *q, void *out, int dtype, const void 
   if (dtype == G2B_F32)
     g2b_launch(attn_generic_kernel<float>, dim3(blocks), dim3(AG_WARPS * 32), 0, stream, 
         (const float *)q, (float *)out, (const float *)cache, tok_pos, tok_seq, page_table, P,
-        n_tokens, nh, nkv, hd, page_size, window, scale, sink, planes, q_stride, (const float *)gate, gate_stride, chunk);
+        n_tokens, nh, nkv, hd, page_size, window, scale, sink, planes, q_stride, (const float *)gate, gate_stride, chunk, (const float *)pooled, pool, pool_rows);
   else if (dtype == G2B_BF16)
     g2b_launch(attn_generic_kernel<bf16>, dim3(blocks), dim3(AG_WARPS * 32), 0, stream, 
         (const bf16 *)q, (bf16 *)out, (const bf16 *)cache, tok_pos, tok_seq, page_table, P,
-        n_tokens, nh, nkv, hd, page_size, window, scale, sink, planes, q_stride, (const bf16 *)gate, gate_stride, chunk);
+        n_tokens, nh, nkv, hd, page_size, window, scale, sink, planes, q_stride, (const bf16 *)gate, gate_stride, chunk, (const bf16 *)pooled, pool, pool_rows);
   else
     G2B_REFUSE("attn_generic: unknown dtype %d", dtype);
   return g2b_check_launch("attn_generic");

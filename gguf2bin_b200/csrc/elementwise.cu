@@ -14,11 +14,11 @@
 G2B_DEFINE_LAST_ERROR
 
 // ---------------------------------------------------------------------------
-// embedding: out[t, :] = table[ids[t], :]   (out is the 32-bit residual stream)
+// embedding: out[t, :] = table[ids[t], :] * scale   (out is the 32-bit residual stream)
 // ---------------------------------------------------------------------------
 template <typename TW>
 __global__ void embed_rows_kernel(const TW *__restrict__ table, const int *__restrict__ ids,
-                                  float *__restrict__ out, int H, int V) {
+                                  float *__restrict__ out, int H, int V, float scale) {
   pdl_launch();
   pdl_wait();
   const int t = blockIdx.x;
@@ -27,18 +27,18 @@ __global__ void embed_rows_kernel(const TW *__restrict__ table, const int *__res
   if (!ok) id = 0;                                   // host validates ids; never read outside
   const TW *row = table + (size_t)id * H;
   float *o = out + (size_t)t * H;
-  for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = ok ? to_f32(row[j]) : 0.f;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = ok ? to_f32(row[j]) * scale : 0.f;
 }
 
 extern "C" int g2b_embed_rows(const void *table, int table_dtype, const int *ids, float *out,
-                              int T, int H, int V, cudaStream_t stream) {
+                              int T, int H, int V, float scale, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H <= 0 || V <= 0) G2B_REFUSE("embed_rows: bad sizes H=%d V=%d", H, V);
   const int threads = H >= 256 ? 256 : 64;
   if (table_dtype == G2B_F32)
-    g2b_launch(embed_rows_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float *)table, ids, out, H, V);
+    g2b_launch(embed_rows_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float *)table, ids, out, H, V, scale);
   else if (table_dtype == G2B_BF16)
-    g2b_launch(embed_rows_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const bf16 *)table, ids, out, H, V);
+    g2b_launch(embed_rows_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const bf16 *)table, ids, out, H, V, scale);
   else
     G2B_REFUSE("embed_rows: unknown table dtype %d", table_dtype);
   return g2b_check_launch("embed_rows");
@@ -245,7 +245,7 @@ extern "C" int g2b_rmsnorm(const float *x, const float *w, const int *rows, int 
 // cos and sin of pos * inv_freq[j] for every token of the step, once per step: all layers
 // with the same frequencies read the same table.  table[t * half + j] = (cos, sin).
 __global__ void rope_table_kernel(const int *__restrict__ tok_pos, const float *__restrict__ inv_freq,
-                                  float2 *__restrict__ table, int T_tokens, int half) {
+                                  float2 *__restrict__ table, int T_tokens, int half, float mult) {
   pdl_launch();
   pdl_wait();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -253,15 +253,15 @@ __global__ void rope_table_kernel(const int *__restrict__ tok_pos, const float *
   const int t = (int)(i / half), j = (int)(i % half);
   float sn, c;
   sincosf((float)tok_pos[t] * inv_freq[j], &sn, &c);
-  table[i] = make_float2(c, sn);
+  table[i] = make_float2(c * mult, sn * mult);
 }
 
 extern "C" int g2b_rope_table(const int *tok_pos, const float *inv_freq, float *table, int T_tokens,
-                              int half, cudaStream_t stream) {
+                              int half, float mult, cudaStream_t stream) {
   if (T_tokens <= 0 || half <= 0) return 0;
   const long long n = (long long)T_tokens * half;
   g2b_launch(rope_table_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, tok_pos, inv_freq,
-             (float2 *)table, T_tokens, half);
+             (float2 *)table, T_tokens, half, mult);
   return g2b_check_launch("rope_table");
 }
 
@@ -568,14 +568,92 @@ extern "C" int g2b_cache_write(const void *k, const void *v, int dtype, int T_to
 }
 
 // ---------------------------------------------------------------------------
+// RMS norm with a token shift: h = w * x / rms(x) for the readers that take the token as it is,
+// and hs = h + (h_prev - h) * mu for the reader that looks one token back.  h_prev is the normed
+// row of the token before in the sequence: the row above in this step, or the sequence's kept row
+// (`state` [slots, H] float; zeros in front of position 0).  The block of a sequence's first row of
+// the step reads the kept row and then replaces it with the normed LAST row of the step, so nobody
+// else touches that slot's place in this launch.  One block per token.
+//   seq_meta [B,4]: first row of the step, rows, tokens before the step, slot; null: one token per
+//   sequence, its position in tok_pos and its slot in seq_slots.
+// ---------------------------------------------------------------------------
+template <typename TO>
+__global__ void __launch_bounds__(256)
+norm_shift_kernel(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ mu,
+                  float *__restrict__ state, const int *__restrict__ tok_seq, const int *__restrict__ tok_pos,
+                  const int *__restrict__ seq_slots, const int *__restrict__ seq_meta,
+                  TO *__restrict__ h_out, TO *__restrict__ hs_out, int H, float eps) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  const int b = tok_seq[t];
+  // without the table of sequences the step is one token per sequence
+  const int first_row = seq_meta ? seq_meta[4 * b + 0] : t, n = seq_meta ? seq_meta[4 * b + 1] : 1;
+  const int past = seq_meta ? seq_meta[4 * b + 2] : tok_pos[t];
+  const int slot = seq_meta ? seq_meta[4 * b + 3] : seq_slots[b];
+  const bool first = t == first_row;
+  const float *xr = x + (size_t)t * H;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) ss = fmaf(xr[j], xr[j], ss);
+  const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)H + eps);
+  float inv_prev = 0.f;
+  const float *xp = xr - H;                          // the row above, where it is the same sequence's
+  if (!first) {
+    float sp = 0.f;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) sp = fmaf(xp[j], xp[j], sp);
+    inv_prev = 1.f / sqrtf(block_sum(sp, scratch) / (float)H + eps);
+  }
+  float *kept = state + (size_t)slot * H;
+  const bool from_state = first && past > 0;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    const float g = w ? w[j] : 1.f;
+    const float h = (g * xr[j]) * inv;
+    const float hp = first ? (from_state ? kept[j] : 0.f) : (g * xp[j]) * inv_prev;
+    h_out[(size_t)t * H + j] = from_f32<TO>(h);
+    hs_out[(size_t)t * H + j] = from_f32<TO>(fmaf(hp - h, mu[j], h));
+  }
+  if (!first) return;
+  // this block alone reads and writes the slot's kept row; every read above is over
+  const float *xl = x + (size_t)(first_row + n - 1) * H;
+  float inv_last = inv;
+  if (n > 1) {
+    float sl = 0.f;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) sl = fmaf(xl[j], xl[j], sl);
+    inv_last = 1.f / sqrtf(block_sum(sl, scratch) / (float)H + eps);
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < H; j += blockDim.x) kept[j] = ((w ? w[j] : 1.f) * xl[j]) * inv_last;
+}
+
+extern "C" int g2b_norm_shift(const float *x, const float *w, const float *mu, float *state, const int *tok_seq,
+                              const int *tok_pos, const int *seq_slots, const int *seq_meta, int T_tokens, int H,
+                              float eps, void *h_out, void *hs_out, int out_dtype, cudaStream_t stream) {
+  if (T_tokens <= 0) return 0;
+  if (!mu || !state || !tok_seq || (!seq_meta && (!tok_pos || !seq_slots)))
+    G2B_REFUSE("norm_shift: shift weights, kept rows and the step's tables are needed");
+  if (out_dtype == G2B_F32)
+    g2b_launch(norm_shift_kernel<float>, dim3(T_tokens), dim3(256), 0, stream, x, w, mu, state, tok_seq, tok_pos, seq_slots, seq_meta,
+               (float *)h_out, (float *)hs_out, H, eps);
+  else if (out_dtype == G2B_BF16)
+    g2b_launch(norm_shift_kernel<bf16>, dim3(T_tokens), dim3(256), 0, stream, x, w, mu, state, tok_seq, tok_pos, seq_slots, seq_meta,
+               (bf16 *)h_out, (bf16 *)hs_out, H, eps);
+  else
+    G2B_REFUSE("norm_shift: unknown output dtype %d", out_dtype);
+  return g2b_check_launch("norm_shift");
+}
+
+// ---------------------------------------------------------------------------
 // SiLU gate on a fused gate/up projection.  Rows of the fused matrix alternate in
 // blocks of `blk`: columns [2*blk*b, 2*blk*b+blk) are gate_{blk*b ..}, the next blk are
 // up_{blk*b ..}; blk == I means "all gates, then all ups".
 //   out[t, i] = (g / (1 + exp(-g))) * u
+// With `limit` > 0 the capped form: g = min(g, limit), u = clamp(u, -limit, limit),
+//   out[t, i] = g / (1 + exp(-alpha g)) * (u + 1)
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void swiglu_kernel(const T *__restrict__ gu, T *__restrict__ out, long long total,
-                              int I, int blk) {
+                              int I, int blk, float limit, float alpha) {
   pdl_launch();
   pdl_wait();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -584,21 +662,27 @@ __global__ void swiglu_kernel(const T *__restrict__ gu, T *__restrict__ out, lon
   const int i = (int)(idx % I);
   const int b = i / blk, r = i % blk;
   const T *row = gu + (size_t)t * 2 * I;
-  const float g = to_f32(row[(size_t)2 * blk * b + r]);
-  const float u = to_f32(row[(size_t)2 * blk * b + blk + r]);
+  float g = to_f32(row[(size_t)2 * blk * b + r]);
+  float u = to_f32(row[(size_t)2 * blk * b + blk + r]);
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    out[idx] = from_f32<T>((g / (1.f + expf(-alpha * g))) * (u + 1.f));
+    return;
+  }
   out[idx] = from_f32<T>((g / (1.f + expf(-g))) * u);
 }
 
 extern "C" int g2b_swiglu(const void *gu, int dtype, int T_tokens, int I, int blk, void *out,
-                          cudaStream_t stream) {
+                          float limit, float alpha, cudaStream_t stream) {
   if (T_tokens <= 0) return 0;
   if (I <= 0 || blk <= 0 || I % blk) G2B_REFUSE("swiglu: block %d does not divide width %d", blk, I);
   const long long total = (long long)T_tokens * I;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   if (dtype == G2B_F32)
-    g2b_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float *)gu, (float *)out, total, I, blk);
+    g2b_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float *)gu, (float *)out, total, I, blk, limit, alpha);
   else if (dtype == G2B_BF16)
-    g2b_launch(swiglu_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16 *)gu, (bf16 *)out, total, I, blk);
+    g2b_launch(swiglu_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16 *)gu, (bf16 *)out, total, I, blk, limit, alpha);
   else
     G2B_REFUSE("swiglu: unknown dtype %d", dtype);
   return g2b_check_launch("swiglu");

@@ -3,7 +3,7 @@
 //   moe_route    scores s = softmax(z) over all experts in 32-bit; the `top` largest of s + c
 //                (c: a stored correction that steers the choice only) are chosen, ties to the
 //                lower index; the weights are the chosen experts' s as they are, or divided by
-//                their sum.  idx [T, top], weight [T, top].
+//                their sum; then times `scale`.  idx [T, top], weight [T, top].
 //   moe_plan     the step's (token, choice) pairs grouped by expert: how many rows every expert
 //                gets, where its rows start, which pair sits in which row, and the list of row
 //                tiles that the products walk.  Experts from `n_real` on have no matrices (their
@@ -13,7 +13,7 @@
 //                output is silu(gate) * up.  32-bit accumulation; a row's sum runs over k in
 //                ascending order whatever else is in the tile.
 //   moe_combine  y_t = sum_j weight_tj * (row of pair (t, j), or the token's own input for an
-//                expert without matrices), added in the order of j.
+//                expert without matrices), added in the order of j; stored, or added to what is there.
 //
 // Which row of an expert's range a pair lands in depends on the batch (the plan hands rows out
 // with atomic counters); what is computed for the pair does not: a row of a product depends on
@@ -71,7 +71,7 @@ extern "C" int g2b_moe_gather(const void *A, int dtype, int a_stride, const int 
 #define ROUTE_WARPS 4
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const float *__restrict__ z, const float *__restrict__ correction, int T, int N, int top,
-                 int renormalise, int *__restrict__ idx, float *__restrict__ weight) {
+                 int renormalise, int *__restrict__ idx, float *__restrict__ weight, float scale) {
   pdl_launch();
   pdl_wait();
   extern __shared__ float sm[];                 // per warp: s [N], pick [N]
@@ -110,24 +110,24 @@ moe_route_kernel(const float *__restrict__ z, const float *__restrict__ correcti
     if (at >= N) at = 0;                        // all NaN: never read outside
     if (lane == 0) {
       idx[(size_t)t * top + r] = at;
-      weight[(size_t)t * top + r] = s[at];
+      weight[(size_t)t * top + r] = renormalise ? s[at] : s[at] * scale;
       pick[at] = -INFINITY;
     }
     chosen_sum += s[at];
     __syncwarp();
   }
   if (renormalise && lane == 0)
-    for (int r = 0; r < top; ++r) weight[(size_t)t * top + r] /= chosen_sum;
+    for (int r = 0; r < top; ++r) weight[(size_t)t * top + r] = weight[(size_t)t * top + r] / chosen_sum * scale;
 }
 
 extern "C" int g2b_moe_route(const float *z, const float *correction, int T, int N, int top, int renormalise,
-                             int *idx, float *weight, cudaStream_t stream) {
+                             int *idx, float *weight, float scale, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (top < 1 || top > N) G2B_REFUSE("moe_route: %d choices among %d experts", top, N);
   const size_t smem = (size_t)ROUTE_WARPS * 2 * N * sizeof(float);
   if (smem > 48 * 1024) G2B_REFUSE("moe_route: %d experts are more than a block's shared memory holds", N);
   g2b_launch(moe_route_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, stream, z,
-             correction, T, N, top, renormalise, idx, weight);
+             correction, T, N, top, renormalise, idx, weight, scale);
   return g2b_check_launch("moe_route");
 }
 
@@ -638,7 +638,7 @@ extern "C" int g2b_moe_gemm(const void *A, int dtype, int a_stride, const int *r
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float *__restrict__ rows, const int *__restrict__ pair_row, const float *__restrict__ weight,
-                   const float *__restrict__ x_self, int T, int top, int Hw, float *__restrict__ out) {
+                   const float *__restrict__ x_self, int T, int top, int Hw, float *__restrict__ out, int accumulate) {
   pdl_launch();
   pdl_wait();
   const int t = blockIdx.x;
@@ -649,7 +649,7 @@ moe_combine_kernel(const float *__restrict__ rows, const int *__restrict__ pair_
       const float v = row >= 0 ? rows[(size_t)row * Hw + j] : x_self[(size_t)t * Hw + j];
       acc = fmaf(weight[(size_t)t * top + r], v, acc);
     }
-    out[(size_t)t * Hw + j] = acc;
+    out[(size_t)t * Hw + j] = accumulate ? out[(size_t)t * Hw + j] + acc : acc;
   }
 }
 
@@ -714,8 +714,8 @@ extern "C" int g2b_moe_combine_norm_add(const float *rows, const int *pair_row, 
 }
 
 extern "C" int g2b_moe_combine(const float *rows, const int *pair_row, const float *weight, const float *x_self, int T,
-                               int top, int Hw, float *out, cudaStream_t stream) {
+                               int top, int Hw, float *out, int accumulate, cudaStream_t stream) {
   if (T <= 0) return 0;
-  g2b_launch(moe_combine_kernel, dim3(T), dim3(256), 0, stream, rows, pair_row, weight, x_self, T, top, Hw, out);
+  g2b_launch(moe_combine_kernel, dim3(T), dim3(256), 0, stream, rows, pair_row, weight, x_self, T, top, Hw, out, accumulate);
   return g2b_check_launch("moe_combine");
 }

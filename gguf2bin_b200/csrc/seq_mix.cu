@@ -16,8 +16,11 @@
 //   state_scan            per head a state S [D, V], a token at a time:
 //                           decay:  S = a S + k v^T;                     o = S^T q
 //                           delta:  S = g S; u = b (v - S^T k); S += k u^T; o = S^T q
+//                           gated:  S = g S + s k v^T;                   o = S^T q
 //                         with a fixed per head, or g = exp(-exp(A) softplus(x + dt)) and
-//                         b = sigmoid(y) per token and head.  q and k are prepared while they are
+//                         b = sigmoid(y) per token and head, or g and s given per token and head
+//                         (`scan_gates` makes them).  One more column whose value is always 1 may
+//                         ride along (the sum of the weighted keys: a normaliser).  q and k are prepared while they are
 //                         staged: rotated (then k times a constant), or made unit vectors.
 //   head_norm_gate        o / sqrt(mean(o^2) + eps) per head (times a weight), times silu(gate)
 //   gate_mul              o * sigmoid(gate) element by element, heads unpadded
@@ -57,10 +60,10 @@ proj_norm_rope_cache_kernel(const T *__restrict__ qkv, int row_stride, const flo
                             const float *__restrict__ k_w, float eps, const float2 *__restrict__ rope,
                             int rot, int interleaved, const int *__restrict__ tok_pos,
                             const int *__restrict__ tok_seq, const int *__restrict__ page_table, int P,
-                            T *__restrict__ cache, int page_size, T *__restrict__ q_out) {
+                            T *__restrict__ cache, int page_size, T *__restrict__ q_out, float v_norm_eps) {
   pdl_launch();
   pdl_wait();
-  extern __shared__ float sm[];                     // q [nh*D], k [nkv*D]
+  extern __shared__ float sm[];                     // q [nh*D], k [nkv*D], one factor per value head [nkv]
   __shared__ float scratch[32];
   const int t = blockIdx.x;
   const int nq = nh * D, nk = nkv * D;
@@ -91,6 +94,19 @@ proj_norm_rope_cache_kernel(const T *__restrict__ qkv, int row_stride, const flo
     for (int h = warp; h < nh + nkv; h += n_warps) rotate_in_place(sm + (size_t)h * D, cs, rot, interleaved, lane);
     __syncthreads();
   }
+  float *v_inv = sm + nq + nk;                      // value heads divided by their root mean square
+  if (v_norm_eps > 0.f) {
+    for (int h = warp; h < nkv; h += n_warps) {
+      float ss = 0.f;
+      for (int d = lane; d < V; d += 32) {
+        const float v = to_f32(src[nq + nk + h * V + d]) + (bias ? bias[nq + nk + h * V + d] : 0.f);
+        ss = fmaf(v, v, ss);
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) v_inv[h] = 1.f / sqrtf(ss / (float)V + v_norm_eps);
+    }
+    __syncthreads();
+  }
   const int pos = tok_pos[t];
   const int page = page_table[(size_t)tok_seq[t] * P + pos / page_size];
   const int in_page = pos % page_size;
@@ -103,7 +119,9 @@ proj_norm_rope_cache_kernel(const T *__restrict__ qkv, int row_stride, const flo
     T *kd = cache + ((((size_t)page * 2 + 0) * nkv + h) * page_size + in_page) * hd;
     T *vd = cache + ((((size_t)page * 2 + 1) * nkv + h) * page_size + in_page) * hd;
     kd[d] = from_f32<T>(d < D ? xk[h * D + d] : 0.f);
-    vd[d] = from_f32<T>(d < V ? to_f32(src[nq + nk + h * V + d]) + (bias ? bias[nq + nk + h * V + d] : 0.f) : 0.f);
+    float v = d < V ? to_f32(src[nq + nk + h * V + d]) + (bias ? bias[nq + nk + h * V + d] : 0.f) : 0.f;
+    if (v_norm_eps > 0.f) v *= v_inv[h];
+    vd[d] = from_f32<T>(v);
   }
 }
 
@@ -111,23 +129,24 @@ extern "C" int g2b_proj_norm_rope_cache(const void *qkv, int dtype, int row_stri
                                         const float *bias, int nh, int nkv, int D, int V, const float *q_w,
                                         const float *k_w, float eps, const float *rope, int rot, int interleaved,
                                         const int *tok_pos, const int *tok_seq, const int *page_table, int P,
-                                        void *cache, int page_size, void *q_out, cudaStream_t stream) {
+                                        void *cache, int page_size, void *q_out, float v_norm_eps,
+                                        cudaStream_t stream) {
   if (T_tokens <= 0) return 0;
   if (rope && (rot <= 0 || rot > D || (rot & 1))) G2B_REFUSE("proj_norm_rope_cache: %d rotated entries of a head of %d", rot, D);
-  const size_t smem = (size_t)(nh + nkv) * D * sizeof(float);
+  const size_t smem = ((size_t)(nh + nkv) * D + nkv) * sizeof(float);
   if (smem > 200 * 1024) G2B_REFUSE("proj_norm_rope_cache: q and k of %d entries do not fit a block's shared memory", (nh + nkv) * D);
   if (dtype == G2B_F32) {
     auto k = proj_norm_rope_cache_kernel<float>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     g2b_launch(k, dim3(T_tokens), dim3(256), smem, stream, (const float *)qkv, row_stride, bias, nh, nkv, D, V, q_w, k_w,
                eps, (const float2 *)rope, rot, interleaved, tok_pos, tok_seq, page_table, P, (float *)cache, page_size,
-               (float *)q_out);
+               (float *)q_out, v_norm_eps);
   } else if (dtype == G2B_BF16) {
     auto k = proj_norm_rope_cache_kernel<bf16>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     g2b_launch(k, dim3(T_tokens), dim3(256), smem, stream, (const bf16 *)qkv, row_stride, bias, nh, nkv, D, V, q_w, k_w,
                eps, (const float2 *)rope, rot, interleaved, tok_pos, tok_seq, page_table, P, (bf16 *)cache, page_size,
-               (bf16 *)q_out);
+               (bf16 *)q_out, v_norm_eps);
   } else {
     G2B_REFUSE("proj_norm_rope_cache: unknown dtype %d", dtype);
   }
@@ -184,7 +203,7 @@ __global__ void __launch_bounds__(256)
 short_conv_kernel(const T *__restrict__ x, int x_stride, const float *__restrict__ w, T *__restrict__ ring,
                   int taps, int C, int T_tokens, const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
                   const int *__restrict__ seq_slots, const int *__restrict__ seq_meta, int act,
-                  T *__restrict__ out, int out_stride) {
+                  T *__restrict__ out, int out_stride, const float *__restrict__ bias) {
   pdl_launch();
   pdl_wait();
   const int t = blockIdx.x;                        // tokens along x: a step may bring more than 65,535
@@ -194,7 +213,7 @@ short_conv_kernel(const T *__restrict__ x, int x_stride, const float *__restrict
   const int first_row = seq_meta ? seq_meta[4 * b + 0] : t;
   const int past = seq_meta ? seq_meta[4 * b + 2] : pos;
   T *my_ring = ring + (size_t)seq_slots[b] * taps * C;
-  float acc = 0.f;
+  float acc = bias ? bias[c] : 0.f;
   for (int j = 0; j < taps; ++j) {
     const int p = pos - (taps - 1) + j;
     float v = 0.f;
@@ -224,7 +243,8 @@ conv_keep_kernel(const T *__restrict__ x, int x_stride, T *__restrict__ ring, in
 
 extern "C" int g2b_short_conv(const void *x, int dtype, int x_stride, const float *w, void *ring, int taps, int C,
                               int T_tokens, int n_seqs, const int *tok_pos, const int *tok_seq, const int *seq_slots,
-                              const int *seq_meta, int act, void *out, int out_stride, cudaStream_t stream) {
+                              const int *seq_meta, int act, void *out, int out_stride, const float *bias,
+                              cudaStream_t stream) {
   if (T_tokens <= 0 || C <= 0) return 0;
   if (taps < 1 || taps > CONV_MAX_TAPS) G2B_REFUSE("short_conv: %d taps outside 1..%d", taps, CONV_MAX_TAPS);
   if (taps > 1 && !ring) G2B_REFUSE("short_conv: no ring for the rows before the step");
@@ -232,13 +252,13 @@ extern "C" int g2b_short_conv(const void *x, int dtype, int x_stride, const floa
   if (grid.y > 65535 || n_seqs > 65535) G2B_REFUSE("short_conv: %d channels or %d sequences are too many for one launch", C, n_seqs);
   if (dtype == G2B_F32) {
     g2b_launch(short_conv_kernel<float>, grid, dim3(256), 0, stream, (const float *)x, x_stride, w, (float *)ring, taps, C,
-               T_tokens, tok_pos, tok_seq, seq_slots, seq_meta, act, (float *)out, out_stride);
+               T_tokens, tok_pos, tok_seq, seq_slots, seq_meta, act, (float *)out, out_stride, bias);
     if (seq_meta && taps > 1)
       g2b_launch(conv_keep_kernel<float>, keep_grid, dim3(256), 0, stream, (const float *)x, x_stride, (float *)ring, taps, C,
                  n_seqs, seq_meta);
   } else if (dtype == G2B_BF16) {
     g2b_launch(short_conv_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16 *)x, x_stride, w, (bf16 *)ring, taps, C,
-               T_tokens, tok_pos, tok_seq, seq_slots, seq_meta, act, (bf16 *)out, out_stride);
+               T_tokens, tok_pos, tok_seq, seq_slots, seq_meta, act, (bf16 *)out, out_stride, bias);
     if (seq_meta && taps > 1)
       g2b_launch(conv_keep_kernel<bf16>, keep_grid, dim3(256), 0, stream, (const bf16 *)x, x_stride, (bf16 *)ring, taps, C,
                  n_seqs, seq_meta);
@@ -262,7 +282,8 @@ extern "C" int g2b_short_conv(const void *x, int dtype, int x_stride, const floa
 struct ScanArgs {
   const void *q, *k, *v;      // compute type; rows of wider buffers
   int q_stride, k_stride, v_stride;
-  int H, G, D, V;             // value heads, query/key heads, key size, value size
+  int H, G, D, V;             // value heads, query/key heads, key size, columns of a head's state
+  int Vin;                    // value size of a head in `v`; columns from there on take the value 1
   const float2 *rope;         // [T, rot/2] or null
   int rot, interleaved;
   float q_scale, k_scale;     // after rotation / after the unit norm
@@ -270,6 +291,7 @@ struct ScanArgs {
   float unit_eps;
   const float *decay;         // mode 0: [H]
   const float *ab;            // mode 1: [T, 2H] float: decay input x, then write-strength input y
+                              // mode 2: [T, 2H] float: the decay g, then the strength s, as they are
   const float *A_log, *dt_bias;      // mode 1: [H]
   float *state;               // [slots, H, V, D]
   const int *tok_pos, *seq_slots, *seq_meta;
@@ -307,7 +329,8 @@ state_scan_kernel(const ScanArgs a, int L) {
   }
   float decay = 1.f, A = 0.f, dt = 0.f;
   if (MODE == 0) decay = a.decay[h];
-  else { A = expf(a.A_log[h]); dt = a.dt_bias[h]; }
+  else if (MODE == 1) { A = expf(a.A_log[h]); dt = a.dt_bias[h]; }
+  const int Vin = a.Vin;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const T *qg = (const T *)a.q, *kg = (const T *)a.k, *vg = (const T *)a.v;
 
@@ -342,16 +365,17 @@ state_scan_kernel(const ScanArgs a, int L) {
         sq[warp][j] *= fq;
         sk[warp][j] *= fk;
       }
-      if (MODE == 1 && lane == 0) {
+      if (MODE != 0 && lane == 0) {
         const float x = a.ab[(size_t)row * 2 * H + h], y = a.ab[(size_t)row * 2 * H + H + h];
-        sg[warp] = expf(-A * softplus_f(x + dt));
-        sb[warp] = sigmoid_f(y);
+        sg[warp] = MODE == 1 ? expf(-A * softplus_f(x + dt)) : x;
+        sb[warp] = MODE == 1 ? sigmoid_f(y) : y;
       }
     }
     for (int i = threadIdx.x; i < nt * cols; i += SCAN_THREADS) {
       const int tt = i / cols, cc = i % cols;
       const int col = blockIdx.x * cols + cc;
-      sv[tt][cc] = col < V ? to_f32(vg[(size_t)(first_row + t0 + tt) * a.v_stride + (size_t)h * V + col]) : 0.f;
+      sv[tt][cc] = col < Vin ? to_f32(vg[(size_t)(first_row + t0 + tt) * a.v_stride + (size_t)h * Vin + col])
+                             : (col < V ? 1.f : 0.f);
     }
     __syncthreads();
     for (int tt = 0; tt < nt; ++tt) {
@@ -365,6 +389,17 @@ state_scan_kernel(const ScanArgs a, int L) {
             const int d = r * L + lane_in_col;
             const float kd = d < D ? kq[d] : 0.f, qd = d < D ? qq[d] : 0.f;
             S[r] = fmaf(decay, S[r], kd * v);
+            o = fmaf(S[r], qd, o);
+          }
+        }
+      } else if (MODE == 2) {
+        const float g = sg[tt], sv_ = sb[tt] * v;
+#pragma unroll
+        for (int r = 0; r < SCAN_R; ++r) {
+          if (r < R) {
+            const int d = r * L + lane_in_col;
+            const float kd = d < D ? kq[d] : 0.f, qd = d < D ? qq[d] : 0.f;
+            S[r] = fmaf(g, S[r], kd * sv_);
             o = fmaf(S[r], qd, o);
           }
         }
@@ -409,17 +444,19 @@ extern "C" int g2b_state_scan(int mode, int dtype, const void *q, int q_stride, 
                               int interleaved, float q_scale, float k_scale, int unit_norm, float unit_eps,
                               const float *decay, const float *ab, const float *A_log, const float *dt_bias,
                               float *state, const int *tok_pos, const int *seq_slots, const int *seq_meta,
-                              int n_tokens, int n_seqs, float *out, cudaStream_t stream) {
+                              int n_tokens, int n_seqs, float *out, int extra_one, cudaStream_t stream) {
   if (n_tokens <= 0 || n_seqs <= 0) return 0;
   if (D <= 0 || D > SCAN_MAX_D) G2B_REFUSE("state_scan: key size %d outside 1..%d", D, SCAN_MAX_D);
   if (G <= 0 || H % G) G2B_REFUSE("state_scan: %d heads are not a multiple of %d query/key heads", H, G);
   if (rope && (rot <= 0 || rot > D || (rot & 1))) G2B_REFUSE("state_scan: %d rotated entries of a head of %d", rot, D);
-  if (mode == 0 ? !decay : (!ab || !A_log || !dt_bias)) G2B_REFUSE("state_scan: mode %d lacks its decay inputs", mode);
+  if (mode == 0 ? !decay : (mode == 1 ? (!ab || !A_log || !dt_bias) : !ab)) G2B_REFUSE("state_scan: mode %d lacks its decay inputs", mode);
+  const int Vin = V;
+  V += extra_one ? 1 : 0;
   int L = 8;
   while (L * SCAN_R < D) L <<= 1;                 // 8, 16 or 32 lanes a column
   ScanArgs a;
   a.q = q; a.k = k; a.v = v; a.q_stride = q_stride; a.k_stride = k_stride; a.v_stride = v_stride;
-  a.H = H; a.G = G; a.D = D; a.V = V; a.rope = (const float2 *)rope; a.rot = rot; a.interleaved = interleaved;
+  a.H = H; a.G = G; a.D = D; a.V = V; a.Vin = Vin; a.rope = (const float2 *)rope; a.rot = rot; a.interleaved = interleaved;
   a.q_scale = q_scale; a.k_scale = k_scale; a.unit_norm = unit_norm; a.unit_eps = unit_eps; a.decay = decay;
   a.ab = ab; a.A_log = A_log; a.dt_bias = dt_bias; a.state = state; a.tok_pos = tok_pos; a.seq_slots = seq_slots;
   a.seq_meta = seq_meta; a.out = out; a.n_tokens = n_tokens;
@@ -432,6 +469,9 @@ extern "C" int g2b_state_scan(int mode, int dtype, const void *q, int q_stride, 
   } else if (mode == 1) {
     if (dtype == G2B_F32) g2b_launch(state_scan_kernel<float, 1>, grid, dim3(SCAN_THREADS), 0, stream, a, L);
     else g2b_launch(state_scan_kernel<bf16, 1>, grid, dim3(SCAN_THREADS), 0, stream, a, L);
+  } else if (mode == 2) {
+    if (dtype == G2B_F32) g2b_launch(state_scan_kernel<float, 2>, grid, dim3(SCAN_THREADS), 0, stream, a, L);
+    else g2b_launch(state_scan_kernel<bf16, 2>, grid, dim3(SCAN_THREADS), 0, stream, a, L);
   } else {
     G2B_REFUSE("state_scan: unknown mode %d", mode);
   }
@@ -498,7 +538,7 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 struct PScanArgs {
   const float *qf, *kf;       // [T, G, D] prepared
   const void *v;              // compute type, rows of a wider buffer
-  int v_stride, H, G, D, V;
+  int v_stride, H, G, D, V, Vin;        // V: columns of a head's state; Vin: value size in `v` (columns beyond: 1)
   const float *decay, *ab, *A_log, *dt_bias;
   float *state;               // [slots, H, V, D]
   const int *seq_meta;
@@ -537,7 +577,8 @@ state_scan_prompt_kernel(const PScanArgs a) {
     }
   float decay = 1.f, A = 0.f, dt = 0.f;
   if (MODE == 0) decay = a.decay[h];
-  else { A = expf(a.A_log[h]); dt = a.dt_bias[h]; }
+  else if (MODE == 1) { A = expf(a.A_log[h]); dt = a.dt_bias[h]; }
+  const int Vin = a.Vin;
   const T *vg = (const T *)a.v;
   for (int i = threadIdx.x; i < 2 * qk_buf; i += PSCAN_THREADS) psm[i] = 0.f;     // rows from D on stay zero
   __syncthreads();
@@ -569,13 +610,15 @@ state_scan_prompt_kernel(const PScanArgs a) {
   auto load_small = [&](int t0, int nt) {
     {
       const int i = threadIdx.x, tt = i / cols, col = blockIdx.x * cols + i % cols;
-      rv0 = (tt < nt && col < V) ? to_f32(vg[(size_t)(first_row + t0 + tt) * a.v_stride + (size_t)h * V + col]) : 0.f;
+      rv0 = (tt < nt && col < Vin) ? to_f32(vg[(size_t)(first_row + t0 + tt) * a.v_stride + (size_t)h * Vin + col])
+                                   : ((tt < nt && col < V) ? 1.f : 0.f);
     }
     {
       const int i = threadIdx.x + PSCAN_THREADS, tt = i / cols, col = blockIdx.x * cols + i % cols;
-      rv1 = (tt < nt && col < V) ? to_f32(vg[(size_t)(first_row + t0 + tt) * a.v_stride + (size_t)h * V + col]) : 0.f;
+      rv1 = (tt < nt && col < Vin) ? to_f32(vg[(size_t)(first_row + t0 + tt) * a.v_stride + (size_t)h * Vin + col])
+                                   : ((tt < nt && col < V) ? 1.f : 0.f);
     }
-    if (MODE == 1 && threadIdx.x < nt) {
+    if (MODE != 0 && threadIdx.x < nt) {
       const size_t row = (size_t)(first_row + t0 + threadIdx.x) * 2 * H;
       rg = a.ab[row + h];
       rb = a.ab[row + H + h];
@@ -585,9 +628,9 @@ state_scan_prompt_kernel(const PScanArgs a) {
     float *dv = small + buf * small_buf;
     if (threadIdx.x < TT * cols) dv[threadIdx.x] = rv0;
     if (threadIdx.x + PSCAN_THREADS < TT * cols) dv[threadIdx.x + PSCAN_THREADS] = rv1;
-    if (MODE == 1 && threadIdx.x < nt) {
-      dv[TT * cols + threadIdx.x] = expf(-A * softplus_f(rg + dt));
-      dv[TT * cols + TT + threadIdx.x] = sigmoid_f(rb);
+    if (MODE != 0 && threadIdx.x < nt) {
+      dv[TT * cols + threadIdx.x] = MODE == 1 ? expf(-A * softplus_f(rg + dt)) : rg;
+      dv[TT * cols + TT + threadIdx.x] = MODE == 1 ? sigmoid_f(rb) : rb;
     }
   };
 
@@ -624,6 +667,20 @@ state_scan_prompt_kernel(const PScanArgs a) {
             S[j][1] = fmaf(decay, S[j][1], kd.y * v);
             S[j][2] = fmaf(decay, S[j][2], kd.z * v);
             S[j][3] = fmaf(decay, S[j][3], kd.w * v);
+            o[j] = fmaf(S[j][3], qd.w, fmaf(S[j][2], qd.z, fmaf(S[j][1], qd.y, S[j][0] * qd.x)));
+          }
+        }
+      } else if (MODE == 2) {
+        const float g = gp[tt], sv_ = bp[tt] * v;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (j < RG) {
+            const float4 kd = *(const float4 *)(kp + 4 * j * L);
+            const float4 qd = *(const float4 *)(qp + 4 * j * L);
+            S[j][0] = fmaf(g, S[j][0], kd.x * sv_);
+            S[j][1] = fmaf(g, S[j][1], kd.y * sv_);
+            S[j][2] = fmaf(g, S[j][2], kd.z * sv_);
+            S[j][3] = fmaf(g, S[j][3], kd.w * sv_);
             o[j] = fmaf(S[j][3], qd.w, fmaf(S[j][2], qd.z, fmaf(S[j][1], qd.y, S[j][0] * qd.x)));
           }
         }
@@ -692,12 +749,14 @@ extern "C" int g2b_state_scan_prompt(int mode, int dtype, const void *q, int q_s
                                      int interleaved, float q_scale, float k_scale, int unit_norm, float unit_eps,
                                      const float *decay, const float *ab, const float *A_log, const float *dt_bias,
                                      float *state, const int *seq_meta, int n_tokens, int n_seqs, float *qf, float *kf,
-                                     float *out, cudaStream_t stream) {
+                                     float *out, int extra_one, cudaStream_t stream) {
   if (n_tokens <= 0 || n_seqs <= 0) return 0;
   if (D <= 0 || D > SCAN_MAX_D) G2B_REFUSE("state_scan: key size %d outside 1..%d", D, SCAN_MAX_D);
   if (G <= 0 || H % G) G2B_REFUSE("state_scan: %d heads are not a multiple of %d query/key heads", H, G);
   if (rope && (rot <= 0 || rot > D || (rot & 1))) G2B_REFUSE("state_scan: %d rotated entries of a head of %d", rot, D);
-  if (mode == 0 ? !decay : (!ab || !A_log || !dt_bias)) G2B_REFUSE("state_scan: mode %d lacks its decay inputs", mode);
+  if (mode == 0 ? !decay : (mode == 1 ? (!ab || !A_log || !dt_bias) : !ab)) G2B_REFUSE("state_scan: mode %d lacks its decay inputs", mode);
+  const int Vin = V;
+  V += extra_one ? 1 : 0;
   if (!seq_meta) G2B_REFUSE("state_scan: the prompt kernel needs the step's table of sequences");
   if (dtype != G2B_F32 && dtype != G2B_BF16) G2B_REFUSE("state_scan: unknown dtype %d", dtype);
   const unsigned prep_blocks = (unsigned)(((long long)n_tokens * G + 3) / 4);
@@ -708,7 +767,7 @@ extern "C" int g2b_state_scan_prompt(int mode, int dtype, const void *q, int q_s
     g2b_launch(scan_prep_kernel<bf16>, dim3(prep_blocks), dim3(128), 0, stream, (const bf16 *)q, q_stride, (const bf16 *)k,
                k_stride, n_tokens, G, D, (const float2 *)rope, rot, interleaved, q_scale, k_scale, unit_norm, unit_eps, qf, kf);
   PScanArgs a;
-  a.qf = qf; a.kf = kf; a.v = v; a.v_stride = v_stride; a.H = H; a.G = G; a.D = D; a.V = V; a.decay = decay; a.ab = ab;
+  a.qf = qf; a.kf = kf; a.v = v; a.v_stride = v_stride; a.H = H; a.G = G; a.D = D; a.V = V; a.Vin = Vin; a.decay = decay; a.ab = ab;
   a.A_log = A_log; a.dt_bias = dt_bias; a.state = state; a.seq_meta = seq_meta; a.out = out;
   // Lanes per column: at least D / 16; more while the step has few columns, so that every scheduler
   // of the GPU gets a few warps (a token's work in a warp is a chain of short dependent steps).
@@ -729,6 +788,9 @@ extern "C" int g2b_state_scan_prompt(int mode, int dtype, const void *q, int q_s
   } else if (mode == 1) {
     if (dtype == G2B_F32) launch_scan_prompt<float, 1>(a, grid, smem, stream);
     else launch_scan_prompt<bf16, 1>(a, grid, smem, stream);
+  } else if (mode == 2) {
+    if (dtype == G2B_F32) launch_scan_prompt<float, 2>(a, grid, smem, stream);
+    else launch_scan_prompt<bf16, 2>(a, grid, smem, stream);
   } else {
     G2B_REFUSE("state_scan: unknown mode %d", mode);
   }
@@ -876,4 +938,263 @@ extern "C" int g2b_norm_add(float *x, const float *y, const float *w, float eps,
   else
     G2B_REFUSE("norm_add: unknown dtype %d", dtype);
   return g2b_check_launch("norm_add");
+}
+
+// ---------------------------------------------------------------------------
+// decays and strengths of the gated scan, per token and head, 32-bit
+// ---------------------------------------------------------------------------
+// Step size of a state-space head: dt = softplus(x + dt_bias); g = exp(-exp(A_log) dt); s = dt.
+// gates [T, 2H]: g, then s.
+template <typename T>
+__global__ void __launch_bounds__(256)
+scan_gates_step_kernel(const T *__restrict__ x, int x_stride, const float *__restrict__ A_log,
+                       const float *__restrict__ dt_bias, int T_tokens, int H, float *__restrict__ gates) {
+  pdl_launch();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)T_tokens * H) return;
+  const int t = (int)(i / H), h = (int)(i % H);
+  const float dt = softplus_f(to_f32(x[(size_t)t * x_stride + h]) + dt_bias[h]);
+  gates[(size_t)t * 2 * H + h] = expf(-expf(A_log[h]) * dt);
+  gates[(size_t)t * 2 * H + H + h] = dt;
+}
+
+extern "C" int g2b_scan_gates_step(const void *x, int dtype, int x_stride, const float *A_log, const float *dt_bias,
+                                   int T_tokens, int H, float *gates, cudaStream_t stream) {
+  if (T_tokens <= 0 || H <= 0) return 0;
+  const unsigned blocks = (unsigned)(((long long)T_tokens * H + 255) / 256);
+  if (dtype == G2B_F32)
+    g2b_launch(scan_gates_step_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float *)x, x_stride, A_log, dt_bias,
+               T_tokens, H, gates);
+  else if (dtype == G2B_BF16)
+    g2b_launch(scan_gates_step_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16 *)x, x_stride, A_log, dt_bias,
+               T_tokens, H, gates);
+  else
+    G2B_REFUSE("scan_gates_step: unknown dtype %d", dtype);
+  return g2b_check_launch("scan_gates_step");
+}
+
+// Exponential gates held stable by a running maximum m (kept per slot and head, from 0):
+//   i = cap tanh((x_i + b_i) / cap);  f = logsigmoid(cap tanh((x_f + b_f) / cap));
+//   m' = max(f + m, i);  g = exp(f + m - m');  s = exp(i - m').
+// gates [T, 2H]: g, then s; m_out [T, H]: m' of every token.  A block walks one sequence's tokens
+// in tiles: the gates of a tile side by side, the chain of maxima by one thread per head, then the
+// exponentials side by side again; the chain depends on the tokens before in the sequence only.
+#define GATES_TILE 1024       // (token, head) pairs of a tile
+template <typename T>
+__global__ void __launch_bounds__(256)
+scan_gates_max_kernel(const T *__restrict__ xi, const T *__restrict__ xf, int x_stride, const float *__restrict__ bi,
+                      const float *__restrict__ bf, float cap, int H, float *__restrict__ m_state,
+                      const int *__restrict__ seq_slots, const int *__restrict__ seq_meta,
+                      float *__restrict__ gates, float *__restrict__ m_out) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float si[GATES_TILE], sf[GATES_TILE], sm_new[GATES_TILE], sm_old[GATES_TILE];
+  const int b = blockIdx.x;
+  const int first_row = seq_meta ? seq_meta[4 * b + 0] : b, n = seq_meta ? seq_meta[4 * b + 1] : 1;
+  const int slot = seq_meta ? seq_meta[4 * b + 3] : seq_slots[b];
+  const int tile = max(1, GATES_TILE / H);
+  const float inv_cap = 1.f / cap;
+  for (int h0 = 0; h0 < H; h0 += GATES_TILE) {       // more heads than a tile holds: in turns
+    const int Hn = min(GATES_TILE, H - h0);
+    float m = threadIdx.x < Hn ? m_state[(size_t)slot * H + h0 + threadIdx.x] : 0.f;
+    float m_hi[GATES_TILE / 256];                     // heads beyond the block's threads
+#pragma unroll
+    for (int e = 1; e < GATES_TILE / 256; ++e) {
+      const int hh = threadIdx.x + 256 * e;
+      m_hi[e] = hh < Hn ? m_state[(size_t)slot * H + h0 + hh] : 0.f;
+    }
+    for (int t0 = 0; t0 < n; t0 += tile) {
+      const int nt = min(tile, n - t0);
+      __syncthreads();
+      for (int idx = threadIdx.x; idx < nt * Hn; idx += blockDim.x) {
+        const int tt = idx / Hn, h = h0 + idx % Hn;
+        const size_t row = (size_t)(first_row + t0 + tt) * x_stride;
+        const float zi = to_f32(xi[row + h]) + bi[h], zf = to_f32(xf[row + h]) + bf[h];
+        si[idx] = cap * tanhf(zi * inv_cap);
+        const float u = cap * tanhf(zf * inv_cap);
+        sf[idx] = fminf(u, 0.f) - log1pf(expf(-fabsf(u)));
+      }
+      __syncthreads();
+#pragma unroll
+      for (int e = 0; e < GATES_TILE / 256; ++e) {
+        const int hh = threadIdx.x + 256 * e;
+        if (hh < Hn) {
+          float mm = e == 0 ? m : m_hi[e];
+          for (int tt = 0; tt < nt; ++tt) {
+            const int idx = tt * Hn + hh;
+            sm_old[idx] = mm;
+            mm = fmaxf(sf[idx] + mm, si[idx]);
+            sm_new[idx] = mm;
+          }
+          if (e == 0) m = mm; else m_hi[e] = mm;
+        }
+      }
+      __syncthreads();
+      for (int idx = threadIdx.x; idx < nt * Hn; idx += blockDim.x) {
+        const int tt = idx / Hn, h = h0 + idx % Hn;
+        const size_t row = (size_t)(first_row + t0 + tt);
+        gates[row * 2 * H + h] = expf(sf[idx] + sm_old[idx] - sm_new[idx]);
+        gates[row * 2 * H + H + h] = expf(si[idx] - sm_new[idx]);
+        m_out[row * H + h] = sm_new[idx];
+      }
+    }
+    if (threadIdx.x < Hn) m_state[(size_t)slot * H + h0 + threadIdx.x] = m;
+#pragma unroll
+    for (int e = 1; e < GATES_TILE / 256; ++e) {
+      const int hh = threadIdx.x + 256 * e;
+      if (hh < Hn) m_state[(size_t)slot * H + h0 + hh] = m_hi[e];
+    }
+  }
+}
+
+extern "C" int g2b_scan_gates_max(const void *xi, const void *xf, int dtype, int x_stride, const float *bi,
+                                  const float *bf, float cap, int H, float *m_state, const int *seq_slots,
+                                  const int *seq_meta, int n_seqs, float *gates, float *m_out, cudaStream_t stream) {
+  if (n_seqs <= 0 || H <= 0) return 0;
+  if (!(cap > 0.f)) G2B_REFUSE("scan_gates_max: the gates' cap must be positive");
+  if (!seq_meta && !seq_slots) G2B_REFUSE("scan_gates_max: neither the step's table of sequences nor their slots");
+  if (dtype == G2B_F32)
+    g2b_launch(scan_gates_max_kernel<float>, dim3(n_seqs), dim3(256), 0, stream, (const float *)xi, (const float *)xf,
+               x_stride, bi, bf, cap, H, m_state, seq_slots, seq_meta, gates, m_out);
+  else if (dtype == G2B_BF16)
+    g2b_launch(scan_gates_max_kernel<bf16>, dim3(n_seqs), dim3(256), 0, stream, (const bf16 *)xi, (const bf16 *)xf,
+               x_stride, bi, bf, cap, H, m_state, seq_slots, seq_meta, gates, m_out);
+  else
+    G2B_REFUSE("scan_gates_max: unknown dtype %d", dtype);
+  return g2b_check_launch("scan_gates_max");
+}
+
+// ---------------------------------------------------------------------------
+// what is read out of a scan, made ready for the output product
+// ---------------------------------------------------------------------------
+// o [T, H, Vs] float, Vs >= V (a head's columns from V on are not output).  Per element j = h V + c:
+//   y = o[h, c]
+//   m given:      y /= max(|o[h, V]|, exp(-m[t, h])) + den_eps      (column V: the normaliser's read-out)
+//   skip given:   y += skip_w[h] * x[j]
+//   gate_first:   y *= act(gate[j])
+//   y /= sqrt(mean over the element's group of `group` elements of y^2 + eps)
+//   y *= w[j mod w_len];  not gate_first: y *= act(gate[j])
+// act: 0 silu, 1 sigmoid.  One warp per (token, group).
+template <typename T>
+__global__ void __launch_bounds__(128)
+state_readout_kernel(const float *__restrict__ o, int T_tokens, int H, int V, int Vs, const float *__restrict__ m,
+                     float den_eps, const T *__restrict__ x, int x_stride, const float *__restrict__ skip_w,
+                     const T *__restrict__ gate, int gate_stride, int gate_act, int gate_first, int group, float eps,
+                     const float *__restrict__ w, int w_len, T *__restrict__ out) {
+  pdl_launch();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = H * V, groups = n / group;
+  const long long item = (long long)blockIdx.x * 4 + warp;
+  if (item >= (long long)T_tokens * groups) return;
+  const int t = (int)(item / groups), j0 = (int)(item % groups) * group;
+  const float *ot = o + (size_t)t * H * Vs;
+  auto value = [&](int j) -> float {
+    const int h = j / V, c = j - h * V;
+    float y = ot[h * Vs + c];
+    if (m) y /= fmaxf(fabsf(ot[h * Vs + V]), expf(-m[(size_t)t * H + h])) + den_eps;
+    if (skip_w) y = fmaf(skip_w[h], to_f32(x[(size_t)t * x_stride + j]), y);
+    if (gate && gate_first) {
+      const float z = to_f32(gate[(size_t)t * gate_stride + j]);
+      y *= gate_act ? sigmoid_f(z) : silu_f(z);
+    }
+    return y;
+  };
+  float ss = 0.f;
+  for (int e = lane; e < group; e += 32) {
+    const float y = value(j0 + e);
+    ss = fmaf(y, y, ss);
+  }
+  const float inv = 1.f / sqrtf(warp_sum(ss) / (float)group + eps);
+  for (int e = lane; e < group; e += 32) {
+    const int j = j0 + e;
+    float y = value(j) * inv;
+    if (w) y *= w[j % w_len];
+    if (gate && !gate_first) {
+      const float z = to_f32(gate[(size_t)t * gate_stride + j]);
+      y *= gate_act ? sigmoid_f(z) : silu_f(z);
+    }
+    out[(size_t)t * n + j] = from_f32<T>(y);
+  }
+}
+
+extern "C" int g2b_state_readout(const float *o, int T_tokens, int H, int V, int Vs, const float *m, float den_eps,
+                                 const void *x, int x_stride, const float *skip_w, const void *gate, int gate_stride,
+                                 int gate_act, int gate_first, int group, float eps, const float *w, int w_len,
+                                 int dtype, void *out, cudaStream_t stream) {
+  if (T_tokens <= 0) return 0;
+  if (group <= 0 || (H * V) % group) G2B_REFUSE("state_readout: groups of %d do not divide %d outputs", group, H * V);
+  if (Vs < V || (m && Vs <= V)) G2B_REFUSE("state_readout: %d stored columns a head for %d outputs", Vs, V);
+  if (w && w_len <= 0) G2B_REFUSE("state_readout: a weight of %d entries", w_len);
+  if (skip_w && !x) G2B_REFUSE("state_readout: a skip weight without its input");
+  const unsigned blocks = (unsigned)(((long long)T_tokens * (H * V / group) + 3) / 4);
+  if (dtype == G2B_F32)
+    g2b_launch(state_readout_kernel<float>, dim3(blocks), dim3(128), 0, stream, o, T_tokens, H, V, Vs, m, den_eps,
+               (const float *)x, x_stride, skip_w, (const float *)gate, gate_stride, gate_act, gate_first, group, eps, w,
+               w_len, (float *)out);
+  else if (dtype == G2B_BF16)
+    g2b_launch(state_readout_kernel<bf16>, dim3(blocks), dim3(128), 0, stream, o, T_tokens, H, V, Vs, m, den_eps,
+               (const bf16 *)x, x_stride, skip_w, (const bf16 *)gate, gate_stride, gate_act, gate_first, group, eps, w,
+               w_len, (bf16 *)out);
+  else
+    G2B_REFUSE("state_readout: unknown dtype %d", dtype);
+  return g2b_check_launch("state_readout");
+}
+
+// ---------------------------------------------------------------------------
+// means of whole blocks of keys and values, kept beside the pages
+// ---------------------------------------------------------------------------
+// A token that ends a block of `pool` positions (pos + 1 a multiple of pool) writes the mean of the
+// block's keys and of its values, read back from the pages as they hold them.  Block b lies in the
+// page of its first position, page_table[(b pool) / page_size], at row b - ceil(first position of
+// that page / pool); a page of the pooled store has `rows` rows: [pages, 2, nkv, rows, hd].
+template <typename T>
+__global__ void __launch_bounds__(128)
+pool_update_kernel(const T *__restrict__ cache, T *__restrict__ pooled, const int *__restrict__ tok_pos,
+                   const int *__restrict__ tok_seq, const int *__restrict__ page_table, int P, int nkv, int hd,
+                   int page_size, int pool, int rows) {
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.x, kvh = blockIdx.y;
+  const int pos = tok_pos[t];
+  if ((pos + 1) % pool) return;
+  const int b = (pos + 1) / pool - 1;
+  const int *pt = page_table + (size_t)tok_seq[t] * P;
+  const int home = (b * pool) / page_size;
+  const int row = b - (home * page_size + pool - 1) / pool;
+  const size_t panel = (size_t)page_size * hd, ppanel = (size_t)rows * hd;
+  const float inv = 1.f / (float)pool;
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float sk = 0.f, sv = 0.f;
+    for (int r = 0; r < pool; ++r) {
+      const int p = b * pool + r;
+      const size_t page = (size_t)pt[p / page_size];
+      const size_t at = (size_t)(p % page_size) * hd + d;
+      sk += to_f32(cache[((page * 2 + 0) * nkv + kvh) * panel + at]);
+      sv += to_f32(cache[((page * 2 + 1) * nkv + kvh) * panel + at]);
+    }
+    const size_t page = (size_t)pt[home];
+    pooled[((page * 2 + 0) * nkv + kvh) * ppanel + (size_t)row * hd + d] = from_f32<T>(sk * inv);
+    pooled[((page * 2 + 1) * nkv + kvh) * ppanel + (size_t)row * hd + d] = from_f32<T>(sv * inv);
+  }
+}
+
+extern "C" int g2b_pool_update(const void *cache, void *pooled, int dtype, const int *tok_pos, const int *tok_seq,
+                               const int *page_table, int P, int T_tokens, int nkv, int hd, int page_size, int pool,
+                               int rows, cudaStream_t stream) {
+  if (T_tokens <= 0) return 0;
+  if (pool <= 0 || rows < (page_size + pool - 1) / pool)
+    G2B_REFUSE("pool_update: %d rows a page do not hold the blocks of %d positions of a page of %d", rows, pool, page_size);
+  if (nkv > 65535) G2B_REFUSE("pool_update: %d kv heads are too many for one launch", nkv);
+  const dim3 grid(T_tokens, nkv);
+  if (dtype == G2B_F32)
+    g2b_launch(pool_update_kernel<float>, grid, dim3(128), 0, stream, (const float *)cache, (float *)pooled, tok_pos, tok_seq,
+               page_table, P, nkv, hd, page_size, pool, rows);
+  else if (dtype == G2B_BF16)
+    g2b_launch(pool_update_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16 *)cache, (bf16 *)pooled, tok_pos, tok_seq,
+               page_table, P, nkv, hd, page_size, pool, rows);
+  else
+    G2B_REFUSE("pool_update: unknown dtype %d", dtype);
+  return g2b_check_launch("pool_update");
 }

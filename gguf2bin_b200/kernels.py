@@ -20,7 +20,7 @@ __all__ = ["KernelError", "KernelBuildError", "embed_rows", "rmsnorm", "qknorm_r
            "attention", "sample_rows", "sample_filtered", "recent_set", "seed_slots", "embed_pair_norm",
            "canon_conv", "norm_canon_single", "latent_keep", "head_product", "head_gate", "gated_add", "xielu",
            "proj_norm_rope_cache", "rotate_heads", "short_conv", "state_scan", "head_norm_gate", "gate_mul",
-           "norm_add", "moe_route", "moe_plan", "moe_gemm", "moe_gemv", "moe_gather", "moe_gemm_tc", "moe_combine", "moe_combine_norm_add", "moe_tile_rows"]
+           "norm_add", "norm_shift", "scan_gates_step", "scan_gates_max", "state_readout", "pool_update", "moe_route", "moe_plan", "moe_gemm", "moe_gemv", "moe_gather", "moe_gemm_tc", "moe_combine", "moe_combine_norm_add", "moe_tile_rows"]
 
 F32, BF16 = 0, 1
 EPI_STORE_F32, EPI_STORE_BF16, EPI_ACCUM_F32 = 0, 1, 2
@@ -125,14 +125,14 @@ def _call(f, *args) -> None:
 # ---------------------------------------------------------------------------
 # elementwise.cu
 # ---------------------------------------------------------------------------
-def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t] = table[ids[t]] widened to float32.  ids int32 [T], out float32 [T, H]."""
+def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t] = table[ids[t]] widened to float32, times ``scale``.  ids int32 [T], out float32 [T, H]."""
     _need(ids, torch.int32, "ids")
     _need(out, torch.float32, "out")
     V, H = table.shape
     f = _fn("elementwise.cu", "g2b_embed_rows",
-            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
-    _call(f, _ptr(table), _code(table.dtype), _ptr(ids), _ptr(out), out.shape[0], H, V, _stream())
+            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    _call(f, _ptr(table), _code(table.dtype), _ptr(ids), _ptr(out), out.shape[0], H, V, float(scale), _stream())
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
@@ -150,13 +150,13 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
     _call(f, _ptr(x), _ptr(w), _ptr(rows), n_rows, H, eps, _ptr(out), _code(out.dtype), _stream())
 
 
-def rope_table(tok_pos: torch.Tensor, inv_freq: torch.Tensor, table: torch.Tensor) -> None:
-    """table[t, j] = (cos, sin)(tok_pos[t] * inv_freq[j]) in float32; table [T, half, 2]."""
+def rope_table(tok_pos: torch.Tensor, inv_freq: torch.Tensor, table: torch.Tensor, mult: float = 1.0) -> None:
+    """table[t, j] = (cos, sin)(tok_pos[t] * inv_freq[j]) * mult in float32; table [T, half, 2]."""
     _need(tok_pos, torch.int32, "tok_pos")
     _need(inv_freq, torch.float32, "inv_freq")
     _need(table, torch.float32, "table")
-    f = _fn("elementwise.cu", "g2b_rope_table", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
-    _call(f, _ptr(tok_pos), _ptr(inv_freq), _ptr(table), table.shape[0], inv_freq.shape[0], _stream())
+    f = _fn("elementwise.cu", "g2b_rope_table", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p])
+    _call(f, _ptr(tok_pos), _ptr(inv_freq), _ptr(table), table.shape[0], inv_freq.shape[0], float(mult), _stream())
 
 
 def qknorm_rope_cache(qkv, n_heads, n_kv_heads, head_dim, q_w, k_w, eps, rope, rotary_dim,
@@ -193,13 +193,35 @@ def cache_write(k, v, n_kv_heads, head_dim, tok_pos, tok_seq, page_table, cache_
           _ptr(cache_pages), page_size, _stream())
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int) -> None:
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int, limit: float = 0.0, alpha: float = 1.0) -> None:
     """out[t, i] = silu(g_i) * u_i from a fused projection whose columns alternate
-    ``block`` gates and ``block`` ups."""
+    ``block`` gates and ``block`` ups.  ``limit`` > 0: the capped form, g = min(g, limit),
+    u = clamp(u, -limit, limit), out = g * sigmoid(alpha * g) * (u + 1)."""
     T, I = out.shape
     f = _fn("elementwise.cu", "g2b_swiglu",
-            [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
-    _call(f, _ptr(gate_up), _code(gate_up.dtype), T, I, block, _ptr(out), _stream())
+            [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_float, c_void_p])
+    _call(f, _ptr(gate_up), _code(gate_up.dtype), T, I, block, _ptr(out), float(limit), float(alpha), _stream())
+
+
+def norm_shift(x32, w, mu, kept, ctx, eps: float, h_out, hs_out) -> None:
+    """RMS norm of every row of the stream with a token shift: ``h_out`` = w * x / rms(x) and
+    ``hs_out`` = h + (h_prev - h) * mu, h_prev the normed row of the token before in the sequence
+    (``kept`` [slots, H] float32 holds it between steps and is brought up to date; zeros in front of
+    position 0).  32-bit arithmetic; both outputs in the compute type."""
+    _need(x32, torch.float32, "x")
+    _need(mu, torch.float32, "shift weights")
+    _need(kept, torch.float32, "kept rows")
+    if w is not None:
+        _need(w, torch.float32, "norm weight")
+    if h_out.dtype != hs_out.dtype or not h_out.is_contiguous() or not hs_out.is_contiguous():
+        raise KernelError("norm_shift: both outputs contiguous and of one dtype")
+    T, H = x32.shape
+    f = _fn("elementwise.cu", "g2b_norm_shift",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
+             c_void_p, c_void_p, c_int, c_void_p])
+    _call(f, _ptr(x32), _ptr(w), _ptr(mu), _ptr(kept), _ptr(ctx.tok_seq), _ptr(ctx.tok_pos), _ptr(ctx.seq_slots),
+          _ptr(ctx.seq_meta), T, H, float(eps),
+          _ptr(h_out), _ptr(hs_out), _code(h_out.dtype), _stream())
 
 
 def advance_positions(tok_pos: torch.Tensor, n: int) -> None:
@@ -438,17 +460,24 @@ def attention_notices(what: str, head_dim: int, page_size: int, compute_dtype: t
 # attention
 # ---------------------------------------------------------------------------
 def attn_generic(q, out, cache_pages, tok_pos, tok_seq, page_table, n_heads, n_kv_heads,
-                 head_dim, page_size, window, scale, sink=None, planes: int = 2, gate=None, chunk: int = 0) -> None:
+                 head_dim, page_size, window, scale, sink=None, planes: int = 2, gate=None, chunk: int = 0,
+                 pooled=None, pool: int = 0) -> None:
     """Causal attention of every token of the step over its sequence's cache pages,
     32-bit arithmetic; q [T, n_heads*head_dim] (rows may lie further apart: columns of a wider
     buffer), out [T, n_heads*head_dim] contiguous.  ``sink`` (float32 [n_heads]): one more
     term exp(sink_h) in each head's softmax denominator.  ``planes`` = 1: the pages hold one
     panel per kv head that is read as keys and as values.  ``gate`` [T, n_heads] (rows may lie
     further apart): every head's output is multiplied by the sigmoid of its gate.  ``chunk`` > 0:
-    a token sees the keys of its own chunk of that many positions only (counted from position 0)."""
+    a token sees the keys of its own chunk of that many positions only (counted from position 0).
+    ``pool`` > 0 with ``pooled`` [pages, 2, kv heads, rows, head_dim] (and a window): in front of the
+    window a token also sees the mean key and value of every block of ``pool`` positions that lies
+    wholly before the window, in the same softmax."""
     f = _fn("attn_generic.cu", "g2b_attn_generic",
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-             c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
+             c_int, c_int, c_void_p])
+    if pool and (pooled is None or pooled.dtype != q.dtype):
+        raise KernelError("attention: pooled blocks need their store, of q's dtype")
     if q.dtype != cache_pages.dtype or out.dtype != q.dtype:
         raise KernelError("attention: q, out and the cache must have one dtype")
     if q.stride(1) != 1 or not out.is_contiguous() or (gate is not None and (gate.stride(1) != 1 or gate.dtype != q.dtype)):
@@ -458,13 +487,22 @@ def attn_generic(q, out, cache_pages, tok_pos, tok_seq, page_table, n_heads, n_k
     _call(f, _ptr(q), _ptr(out), _code(q.dtype), _ptr(cache_pages), _ptr(tok_pos), _ptr(tok_seq),
           _ptr(page_table), page_table.shape[1], q.shape[0], n_heads, n_kv_heads, head_dim,
           page_size, window, scale, _ptr(sink), planes, q.stride(0), _ptr(gate),
-          gate.stride(0) if gate is not None else 0, int(chunk), _stream())
+          gate.stride(0) if gate is not None else 0, int(chunk), _ptr(pooled) if pool else None, int(pool),
+          pooled.shape[3] if pool else 0, _stream())
 
 
 def attention(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
-              scale, sink=None, planes: int = 2, gate=None, chunk: int = 0) -> None:
+              scale, sink=None, planes: int = 2, gate=None, chunk: int = 0, pooled=None, pool: int = 0) -> None:
     """Attention of a step: the tensor-core kernels when they take the case, else the
-    32-bit kernel.  ``q`` and ``gate`` may be column ranges of a wider buffer."""
+    32-bit kernel.  ``q`` and ``gate`` may be column ranges of a wider buffer.  ``pool``, ``pooled``:
+    mean keys and values of whole blocks in front of the window (``attn_generic``)."""
+    if pool:
+        if q.dtype == torch.bfloat16 and (_bf16 or _bf16_mod()).attention_pooled_bf16(
+                q, out, cache_pages, pooled, ctx, n_heads, n_kv_heads, head_dim, page_size, window, pool, scale):
+            return
+        attn_generic(q, out, cache_pages, ctx.tok_pos, ctx.tok_seq, ctx.page_table, n_heads, n_kv_heads, head_dim,
+                     page_size, window, scale, sink, planes, gate, chunk, pooled, pool)
+        return
     if q.dtype == torch.bfloat16:
         if (_bf16 or _bf16_mod()).attention_bf16(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim,
                                        page_size, window, scale, sink, planes, gate, chunk):
@@ -579,14 +617,16 @@ def _dense_rows(t: torch.Tensor, what: str) -> int:
 
 
 def proj_norm_rope_cache(qkv, bias, n_heads, n_kv_heads, qk_dim, v_dim, q_w, k_w, eps, rope, rotary_dim,
-                         interleaved, ctx, cache_pages, page_size, q_out) -> None:
+                         interleaved, ctx, cache_pages, page_size, q_out, v_norm_eps: float = 0.0) -> None:
     """q, k, v side by side in ``qkv`` [T, nh*D + nkv*D + nkv*V] (+ ``bias``, float32); RMS norm over
     ALL of q and over all of k (weights ``q_w`` [nh*D], ``k_w`` [nkv*D]; None: no norm); rotation by
     the step's ``rope`` table, pairs (i, i + r/2) or, ``interleaved``, (2i, 2i + 1); q to ``q_out``
-    [T, nh*hd] and k, v into the pages, heads zero-filled to hd = max(D, V)."""
+    [T, nh*hd] and k, v into the pages, heads zero-filled to hd = max(D, V).  ``v_norm_eps`` > 0: every
+    value head is divided by its root mean square (that eps inside the root) before it is stored."""
     f = _fn("seq_mix.cu", "g2b_proj_norm_rope_cache",
             [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
-             c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p])
+             c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_float,
+             c_void_p])
     if q_out.dtype != qkv.dtype or cache_pages.dtype != qkv.dtype or not q_out.is_contiguous():
         raise KernelError("proj_norm_rope_cache: q_out and the cache must have the input's dtype")
     for t in (bias, q_w, k_w):
@@ -595,7 +635,7 @@ def proj_norm_rope_cache(qkv, bias, n_heads, n_kv_heads, qk_dim, v_dim, q_w, k_w
     _call(f, _ptr(qkv), _code(qkv.dtype), _dense_rows(qkv, "qkv"), qkv.shape[0], _ptr(bias), n_heads, n_kv_heads,
           qk_dim, v_dim, _ptr(q_w), _ptr(k_w), eps, _ptr(rope), rotary_dim, 1 if interleaved else 0,
           _ptr(ctx.tok_pos), _ptr(ctx.tok_seq), _ptr(ctx.page_table), ctx.page_table.shape[1],
-          _ptr(cache_pages), page_size, _ptr(q_out), _stream())
+          _ptr(cache_pages), page_size, _ptr(q_out), float(v_norm_eps), _stream())
 
 
 def rotate_heads(x, heads, head_dim, rope, rotary_dim, interleaved, scale: float = 1.0) -> None:
@@ -607,8 +647,8 @@ def rotate_heads(x, heads, head_dim, rope, rotary_dim, interleaved, scale: float
           1 if interleaved else 0, scale, _stream())
 
 
-def short_conv(x, w32, ring, ctx, out, act: bool = True) -> None:
-    """out_t = act(sum_j w32[j, c] * x_{t - taps + 1 + j}[c]) per channel, act = SiLU; ``w32`` float32
+def short_conv(x, w32, ring, ctx, out, act: bool = True, bias=None) -> None:
+    """out_t = act(bias[c] + sum_j w32[j, c] * x_{t - taps + 1 + j}[c]) per channel, act = SiLU; ``w32`` float32
     [taps, C]; ``ring`` [slots, taps, C] holds every sequence's last input rows by position mod taps
     and is brought up to date (in the same launch for a step of one token per sequence)."""
     taps, C = w32.shape
@@ -617,27 +657,39 @@ def short_conv(x, w32, ring, ctx, out, act: bool = True) -> None:
         raise KernelError("short_conv: input, output and ring must have one dtype")
     f = _fn("seq_mix.cu", "g2b_short_conv",
             [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
-             c_void_p, c_int, c_void_p, c_int, c_void_p])
+             c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p])
+    if bias is not None:
+        _need(bias, torch.float32, "convolution bias")
     _call(f, _ptr(x), _code(x.dtype), _dense_rows(x, "x"), _ptr(w32), _ptr(ring), taps, C, x.shape[0], ctx.n_seqs,
           _ptr(ctx.tok_pos), _ptr(ctx.tok_seq), _ptr(ctx.seq_slots), _ptr(ctx.seq_meta), 1 if act else 0,
-          _ptr(out), _dense_rows(out, "out"), _stream())
+          _ptr(out), _dense_rows(out, "out"), _ptr(bias), _stream())
     if ctx.seq_meta is not None and taps > 1:
         count_launches(1)
 
 
 def state_scan(q, k, v, state, ctx, out32, heads, qk_heads, qk_dim, v_dim, *, decay=None, ab=None, a_log=None,
                dt_bias=None, rope=None, rotary_dim: int = 0, interleaved: bool = False, q_scale: float = 1.0,
-               k_scale: float = 1.0, unit_eps: Optional[float] = None) -> None:
+               k_scale: float = 1.0, unit_eps: Optional[float] = None, gates=None, ones_column: bool = False) -> None:
     """The recurrence of a mixer with a matrix state per head, over the step's tokens in order;
     ``state`` float32 [slots, heads, v_dim, qk_dim] is read and left up to date.  ``decay`` (float32
     [heads]): S = a S + k v^T.  Otherwise ``ab`` (float32 [T, 2*heads]: x then y), ``a_log``, ``dt_bias``:
     S = g S with g = exp(-exp(a_log) softplus(x + dt_bias)); u = sigmoid(y) (v - S^T k); S += k u^T.
+    Or ``gates`` (float32 [T, 2*heads]: a decay g, then a strength s, per token and head, as
+    ``scan_gates_step`` / ``scan_gates_max`` make them): S = g S + s k v^T.
     Either way o = S^T q, float32 into ``out32`` [T, heads*v_dim].  q and k first turn by ``rope``
-    (or, with ``unit_eps``, are divided by sqrt(sum x^2 + unit_eps)), then take their scales."""
+    (or, with ``unit_eps``, are divided by sqrt(sum x^2 + unit_eps)), then take their scales.
+    ``ones_column``: every head carries one more column whose value is 1 at every token (the weighted
+    sum of the keys); state and output then have ``v_dim + 1`` columns a head."""
     T = q.shape[0]
     _need(state, torch.float32, "state")
     _need(out32, torch.float32, "scan output")
-    mode = 0 if decay is not None else 1
+    mode = 0 if decay is not None else (2 if gates is not None else 1)
+    if gates is not None:
+        ab = gates
+    cols = v_dim + (1 if ones_column else 0)
+    if tuple(state.shape[1:]) != (heads, cols, qk_dim) or tuple(out32.shape) != (T, heads * cols):
+        raise KernelError(f"state_scan: state {tuple(state.shape)} or output {tuple(out32.shape)} do not fit "
+                          f"{heads} heads of {cols} columns of {qk_dim}")
     for t in (decay, ab, a_log, dt_bias):
         if t is not None:
             _need(t, torch.float32, "decay inputs")
@@ -655,14 +707,89 @@ def state_scan(q, k, v, state, ctx, out32, heads, qk_heads, qk_dim, v_dim, *, de
         qf = ctx.workspace.buffer("scan.q", (T, qk_heads * qk_dim), torch.float32)
         kf = ctx.workspace.buffer("scan.k", (T, qk_heads * qk_dim), torch.float32)
         f = _fn("seq_mix.cu", "g2b_state_scan_prompt",
-                types + [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
-        _call(f, *common, _ptr(ctx.seq_meta), T, ctx.n_seqs, _ptr(qf), _ptr(kf), _ptr(out32), _stream())
+                types + [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+        _call(f, *common, _ptr(ctx.seq_meta), T, ctx.n_seqs, _ptr(qf), _ptr(kf), _ptr(out32),
+              1 if ones_column else 0, _stream())
         count_launches(1)
         return
     f = _fn("seq_mix.cu", "g2b_state_scan",
-            types + [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p])
+            types + [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p])
     _call(f, *common, _ptr(ctx.tok_pos), _ptr(ctx.seq_slots), _ptr(ctx.seq_meta), T, ctx.n_seqs,
-          _ptr(out32), _stream())
+          _ptr(out32), 1 if ones_column else 0, _stream())
+
+
+def scan_gates_step(x, a_log, dt_bias, gates) -> None:
+    """Decay and strength of a state-space head from its step size: dt = softplus(x + dt_bias),
+    g = exp(-exp(a_log) dt), s = dt; x [T, heads] (columns of a wider buffer), ``gates`` float32
+    [T, 2*heads]: g, then s."""
+    _need(gates, torch.float32, "gates")
+    _need(a_log, torch.float32, "a_log")
+    _need(dt_bias, torch.float32, "dt_bias")
+    T, H = x.shape
+    f = _fn("seq_mix.cu", "g2b_scan_gates_step",
+            [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p])
+    _call(f, _ptr(x), _code(x.dtype), _dense_rows(x, "x"), _ptr(a_log), _ptr(dt_bias), T, H, _ptr(gates), _stream())
+
+
+def scan_gates_max(x_i, x_f, b_i, b_f, cap: float, m_state, ctx, gates, m_out) -> None:
+    """Exponential gates under a running maximum: i = cap tanh((x_i + b_i) / cap),
+    f = logsigmoid(cap tanh((x_f + b_f) / cap)), m' = max(f + m, i), g = exp(f + m - m'),
+    s = exp(i - m'); ``m_state`` float32 [slots, heads] holds m between steps (from 0) and is left
+    up to date; ``gates`` float32 [T, 2*heads]: g, then s; ``m_out`` float32 [T, heads]: m' per token."""
+    for t, what in ((gates, "gates"), (m_out, "m_out"), (m_state, "m_state"), (b_i, "b_i"), (b_f, "b_f")):
+        _need(t, torch.float32, what)
+    if x_i.dtype != x_f.dtype or x_i.stride(0) != x_f.stride(0):
+        raise KernelError("scan_gates_max: both gate inputs are columns of one buffer")
+    H = x_i.shape[1]
+    f = _fn("seq_mix.cu", "g2b_scan_gates_max",
+            [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_void_p, c_int,
+             c_void_p, c_void_p, c_void_p])
+    _call(f, _ptr(x_i), _ptr(x_f), _code(x_i.dtype), _dense_rows(x_i, "x_i"), _ptr(b_i), _ptr(b_f), float(cap), H,
+          _ptr(m_state), _ptr(ctx.seq_slots), _ptr(ctx.seq_meta), ctx.n_seqs, _ptr(gates), _ptr(m_out), _stream())
+
+
+def state_readout(o32, heads, v_dim, out, *, stored_cols: Optional[int] = None, m=None, den_eps: float = 0.0,
+                  skip_x=None, skip_w=None, gate=None, gate_act: str = "silu", gate_first: bool = False,
+                  group: Optional[int] = None, eps: float = 0.0, w=None) -> None:
+    """What a scan reads out, made ready for the output product, 32-bit: with ``m`` [T, heads] every
+    head is divided by max(|its column v_dim|, exp(-m)) + den_eps; ``skip_w`` [heads] times ``skip_x``
+    [T, heads*v_dim] is added; ``gate_first``: times act(gate); then every ``group`` neighbouring
+    outputs (default: a head) are divided by their root mean square (``eps`` inside the root), times
+    ``w`` (one per output, or one head's worth shared by all), times act(gate) if not before.
+    act: "silu" or "sigmoid".  ``out`` [T, heads*v_dim] in the compute type."""
+    _need(o32, torch.float32, "scan output")
+    T = o32.shape[0]
+    Vs = int(stored_cols or v_dim)
+    if gate_act not in ("silu", "sigmoid"):
+        raise KernelError(f"state_readout: gate activation {gate_act!r}")
+    for t in (m, skip_w, w):
+        if t is not None:
+            _need(t, torch.float32, "read-out inputs")
+    for t in (skip_x, gate):
+        if t is not None and t.dtype != out.dtype:
+            raise KernelError("state_readout: skip input and gate must have the output's dtype")
+    f = _fn("seq_mix.cu", "g2b_state_readout",
+            [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+             c_int, c_int, c_float, c_void_p, c_int, c_int, c_void_p, c_void_p])
+    _call(f, _ptr(o32), T, heads, v_dim, Vs, _ptr(m), float(den_eps), _ptr(skip_x),
+          _dense_rows(skip_x, "skip_x") if skip_x is not None else 0, _ptr(skip_w), _ptr(gate),
+          _dense_rows(gate, "gate") if gate is not None else 0, 1 if gate_act == "sigmoid" else 0,
+          1 if gate_first else 0, int(group or v_dim), float(eps), _ptr(w), w.numel() if w is not None else 0,
+          _code(out.dtype), _ptr(out), _stream())
+
+
+def pool_update(cache_pages, pooled_pages, ctx, n_kv_heads, head_dim, page_size, pool: int) -> None:
+    """Every token of the step that ends a block of ``pool`` positions writes the mean of the block's
+    keys and of its values (as the pages hold them) into ``pooled_pages`` [pages, 2, kv heads, rows,
+    head_dim]: block b in the page of its first position, at row b - ceil(that page's first position / pool)."""
+    if pooled_pages.dtype != cache_pages.dtype:
+        raise KernelError("pool_update: both stores must have one dtype")
+    f = _fn("seq_mix.cu", "g2b_pool_update",
+            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+             c_void_p])
+    _call(f, _ptr(cache_pages), _ptr(pooled_pages), _code(cache_pages.dtype), _ptr(ctx.tok_pos), _ptr(ctx.tok_seq),
+          _ptr(ctx.page_table), ctx.page_table.shape[1], ctx.n_tokens, n_kv_heads, head_dim, page_size, int(pool),
+          pooled_pages.shape[3], _stream())
 
 
 def head_norm_gate(o32, heads, v_dim, w, eps, gate, out_scale, out) -> None:
@@ -711,16 +838,17 @@ def moe_tile_rows() -> int:
     return int(lib.g2b_moe_tile_rows())
 
 
-def moe_route(z32, correction, top: int, renormalise: bool, idx, weight) -> None:
+def moe_route(z32, correction, top: int, renormalise: bool, idx, weight, scale: float = 1.0) -> None:
     """softmax over all experts of ``z32`` [T, N]; the ``top`` largest of score + correction chosen
     (``idx`` int32 [T, top]); ``weight`` float32 [T, top] their scores (divided by their sum when
-    ``renormalise``)."""
+    ``renormalise``), times ``scale``."""
     _need(z32, torch.float32, "router logits")
     _need(idx, torch.int32, "idx")
     _need(weight, torch.float32, "weight")
-    f = _fn("moe.cu", "g2b_moe_route", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    f = _fn("moe.cu", "g2b_moe_route", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
+                                        c_void_p])
     _call(f, _ptr(z32), _ptr(correction), z32.shape[0], z32.shape[1], top, 1 if renormalise else 0, _ptr(idx),
-          _ptr(weight), _stream())
+          _ptr(weight), float(scale), _stream())
 
 
 def moe_plan(idx, n_real: int, max_tiles: int, plan, row_pair, pair_row) -> None:
@@ -783,11 +911,13 @@ def moe_gemm_tc(a_rows, w, n_out: int, plan, n_real: int, max_tiles: int, swiglu
     return (_bf16 or _bf16_mod()).gemm_tc_grouped(a_rows, w, n_out, plan, n_real, max_tiles, swiglu, out)
 
 
-def moe_combine(rows32, pair_row, weight, x_self32, top: int, out32) -> None:
-    """out[t] = sum_j weight[t, j] * (rows32[pair_row[t, j]], or x_self32[t] where the pair has no row)."""
-    f = _fn("moe.cu", "g2b_moe_combine", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+def moe_combine(rows32, pair_row, weight, x_self32, top: int, out32, accumulate: bool = False) -> None:
+    """out[t] = sum_j weight[t, j] * (rows32[pair_row[t, j]], or x_self32[t] where the pair has no row);
+    ``accumulate``: added to ``out32`` instead of stored."""
+    f = _fn("moe.cu", "g2b_moe_combine", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int,
+                                          c_void_p])
     _call(f, _ptr(rows32), _ptr(pair_row), _ptr(weight), _ptr(x_self32), out32.shape[0], top, out32.shape[1],
-          _ptr(out32), _stream())
+          _ptr(out32), 1 if accumulate else 0, _stream())
 
 
 def moe_combine_norm_add(rows32, pair_row, weight, x32, norm_w, eps: float, top: int, cast_out=None) -> bool:

@@ -336,6 +336,13 @@ def attention_bf16(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page
     return False
 
 
+def attention_pooled_bf16(q, out, cache_pages, pooled, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
+                          pool, scale) -> bool:
+    """Attention over a window of tokens and the pooled blocks in front of it on the tensor cores;
+    False: the case is left to the 32-bit kernel."""
+    return False
+
+
 USE_TC_ATTENTION = True      # prompt attention on tcgen05 (else the mma.sync kernel)
 
 

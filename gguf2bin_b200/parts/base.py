@@ -62,16 +62,16 @@ class StepContext:
     step_cache: dict = field(default_factory=dict)   # tensors derived once per step (cleared by the model)
     next_block: Optional[object] = None              # the block that runs after the one running now (None: the last)
 
-    def rope_table(self, inv_freq: torch.Tensor) -> torch.Tensor:
-        """(cos, sin) of every token's position times ``inv_freq``, computed once per step and
-        shared by all layers that rotate with these frequencies; float32 [T, half, 2]."""
-        key = ("rope", inv_freq.data_ptr())
+    def rope_table(self, inv_freq: torch.Tensor, mult: float = 1.0) -> torch.Tensor:
+        """(cos, sin) of every token's position times ``inv_freq``, both times ``mult``, computed once
+        per step and shared by all layers that rotate with these frequencies; float32 [T, half, 2]."""
+        key = ("rope", inv_freq.data_ptr(), float(mult))
         table = self.step_cache.get(key)
         if table is None:
             from .. import kernels
             table = self.workspace.buffer(f"rope.table.{len(self.step_cache)}",
                                           (self.n_tokens, inv_freq.shape[0], 2), torch.float32)
-            kernels.rope_table(self.tok_pos[:self.n_tokens], inv_freq, table)
+            kernels.rope_table(self.tok_pos[:self.n_tokens], inv_freq, table, mult)
             self.step_cache[key] = table
         return table
 

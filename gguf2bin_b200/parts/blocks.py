@@ -3,14 +3,16 @@ residual stream kept in float32 (src/l5_model.c:494-597 of AnonymoDGH/gguf2bin).
 ``branch_norm``: x += norm(mixer(x)); x += norm(feed_forward(x)): the norm sits on each sublayer's
 OUTPUT and the sublayers read the stream itself.
 ``gated_prenorm``: the same with each sublayer's result scaled by a learned gate, an optional
-short convolution over time in front of the mixer, and an optional feed-forward."""
+short convolution over time in front of the mixer, and an optional feed-forward.
+``parallel_shift``: h = norm(x); x += mixer(shift(h)) + feed_forward(h): one norm, both sublayers read
+it, and the mixer's copy is mixed with the token before, channel by channel."""
 from __future__ import annotations
 
 import torch
 
 from .. import kernels
 from ..cache.storage import StateNeed
-from ..config.specs import LayerSpec
+from ..config.specs import ConfigError, LayerSpec
 from ..weights.loader import Expected
 from .feed_forward import RoutedExperts
 from .norms import RMSNorm
@@ -367,6 +369,83 @@ class GatedPreNormBlock:
             kernels.gated_add(x32, y, gate, bias)
 
 
+class ParallelShiftBlock:
+    """``parallel_shift``: with h = norm(x), x <- x + mixer(hs) + feed_forward(h).  There is one norm;
+    the feed-forward reads h as it is, the mixer reads hs_t = h_t + (h_{t-1} - h_t) * mu, mu one learned
+    number per channel and h_{t-1} the UNshifted normed row of the token before (zeros in front of a
+    sequence's first token).  The normed row of a sequence's latest token is the block's own state
+    (one row per slot, 32-bit), whatever the mixer keeps.  A layer may have no feed-forward.  Any
+    mixer and feed-forward of the library fit: both add into the stream."""
+
+    def __init__(self, layer: LayerSpec, hidden_size: int, dtype: torch.dtype, device):
+        self.names = dict(layer.block["names"])
+        self.hidden, self.dtype = int(hidden_size), dtype
+        self.norm = norm_class(layer.norm)(layer.norm, hidden_size, dtype, device)
+        if not isinstance(self.norm, RMSNorm):
+            raise ConfigError("parallel_shift: the norm in front of the token shift is an rmsnorm")
+        self.mixer = mixer_class(layer.mixer)(layer.mixer, hidden_size, dtype, device)
+        self.feed_forward = None
+        if layer.feed_forward is not None:
+            self.feed_forward = feed_forward_class(layer.feed_forward)(layer.feed_forward, hidden_size, dtype, device)
+        self.mu = None
+
+    @classmethod
+    def expected(cls, layer: LayerSpec, hidden_size: int) -> dict:
+        names = dict(layer.block["names"])
+        out = {names["shift"]: Expected((int(hidden_size),))}
+        out.update(norm_class(layer.norm).expected(layer.norm, hidden_size, names["norm"]))
+        out.update(mixer_class(layer.mixer).expected(layer.mixer, hidden_size))
+        if layer.feed_forward is not None:
+            out.update(feed_forward_class(layer.feed_forward).expected(layer.feed_forward, hidden_size))
+        return out
+
+    def bind(self, tensors: dict) -> None:
+        self.norm.bind(tensors[self.names["norm"]])
+        self.mu = tensors[self.names["shift"]].to(torch.float32).contiguous()
+        self.mixer.bind(tensors)
+        if self.feed_forward is not None:
+            self.feed_forward.bind(tensors)
+
+    def cache_need(self):
+        need = {"shift": StateNeed((self.hidden,), torch.float32)}
+        own = self.mixer.cache_need()
+        if isinstance(own, dict):
+            need.update({f"mixer.{k}": v for k, v in own.items() if v is not None})
+        elif own is not None:
+            need["mixer"] = own
+        return need
+
+    def parts(self) -> tuple:
+        return tuple(p for p in (self.norm, self.mixer, self.feed_forward) if p is not None)
+
+    def weights(self):
+        for part in self.parts():
+            yield from getattr(part, "weights", tuple)()
+        if self.mu is not None:
+            yield self.mu
+
+    def notices(self) -> list:
+        return [line for part in self.parts() for line in getattr(part, "notices", list)()]
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(part, "graph_safe", False) for part in self.parts())
+
+    def forward(self, x32: torch.Tensor, ctx, cache_view) -> None:
+        T, H, ws = x32.shape[0], self.hidden, ctx.workspace
+        view = cache_view or {}
+        h = ws.buffer("shift.normed", (T, H), self.dtype)
+        hs = ws.buffer("shift.shifted", (T, H), self.dtype)
+        kernels.norm_shift(x32, self.norm.weight, self.mu, view["shift"].states, ctx, self.norm.eps, h, hs)
+        own = view.get("mixer")
+        if own is None:
+            own = {k[len("mixer."):]: v for k, v in view.items() if k.startswith("mixer.")} or None
+        self.mixer.forward(hs, ctx, own, x32)
+        if self.feed_forward is not None:
+            self.feed_forward.forward(h, ctx, x32)
+
+
 register_block("prenorm", PreNormBlock)
+register_block("parallel_shift", ParallelShiftBlock)
 register_block("gated_prenorm", GatedPreNormBlock)
 register_block("branch_norm", BranchNormBlock)

@@ -2,7 +2,7 @@
 into logits.
 
 ``token_embedding``: row ``id`` of the table, widened to float32
-(src/l5_model.c:488-492 of AnonymoDGH/gguf2bin).
+(src/l5_model.c:488-492 of AnonymoDGH/gguf2bin), times ``scale`` when the spec has one.
 ``lm_head``: logits = h . W^T in float32, W a matrix of its own or, when ``tied``, the
 embedding's table (src/l5_model.c:600-605: without an output tensor the reference
 multiplies by the token-embedding matrix).
@@ -28,6 +28,7 @@ class TokenEmbedding:
     def __init__(self, spec: PartSpec, vocab_size: int, hidden_size: int, dtype: torch.dtype, device):
         self.name = spec["name"]
         self.vocab, self.hidden = int(vocab_size), int(hidden_size)
+        self.scale = float(spec.get("scale") if spec.get("scale") is not None else 1.0)
         self.table: Optional[torch.Tensor] = None      # [vocab, hidden]; a tied head multiplies by it
 
     @classmethod
@@ -41,8 +42,8 @@ class TokenEmbedding:
         return (self.table,)
 
     def forward(self, tok_ids: torch.Tensor, out32: torch.Tensor, ctx) -> None:
-        """out32[t] = table[tok_ids[t]] as float32; out32 is [T, hidden]."""
-        kernels.embed_rows(self.table, tok_ids, out32)
+        """out32[t] = table[tok_ids[t]] * scale as float32; out32 is [T, hidden]."""
+        kernels.embed_rows(self.table, tok_ids, out32, self.scale)
 
 
 class LMHead:

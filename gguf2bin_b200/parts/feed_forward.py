@@ -5,6 +5,9 @@ The gate and up matrices are fused into one at bind time, rows alternating in bl
 eight (eight gate rows, then the eight up rows of the same outputs), so one product
 yields both and a kernel finds a gate and its up value sixteen columns apart at most.
 A width that is no multiple of eight keeps the plain order (all gates, then all ups).
+With ``limit`` the gate is capped from above and the up value from both sides, the gate's sigmoid
+takes a slope and the up value an offset of one: g = min(gate x, limit), u = clamp(up x, -limit,
+limit), down( g sigmoid(alpha g) (u + 1) ), ``alpha`` 1.702 unless the spec says otherwise.
 """
 from __future__ import annotations
 
@@ -14,7 +17,7 @@ from .. import kernels
 from ..config.specs import ConfigError, PartSpec
 from ..weights.loader import Expected
 from .fused import normed_linear
-from .registry import register_feed_forward
+from .registry import feed_forward_class, register_feed_forward
 
 
 class SwiGLU:
@@ -27,6 +30,10 @@ class SwiGLU:
         self.dtype = dtype
         self.names = dict(spec["names"])
         self.w_gate_up = self.w_down = None
+        self.limit = float(spec.get("limit") or 0.0)
+        self.alpha = float(spec.get("alpha") if spec.get("alpha") is not None else 1.702)
+        if self.limit < 0:
+            raise ConfigError("swiglu: limit must be positive (or absent)")
 
     @classmethod
     def expected(cls, spec: PartSpec, hidden_size: int) -> dict:
@@ -50,7 +57,7 @@ class SwiGLU:
     def absorb_norm_weight(self, norm) -> bool:
         """As ``GQAAttention.absorb_norm_weight``, into the columns of the gate/up matrix."""
         if self.dtype != torch.bfloat16 or self.w_gate_up.dtype != torch.bfloat16 or self.block != 8 \
-                or not hasattr(norm, "give_up_weight"):
+                or not hasattr(norm, "give_up_weight") or self.limit:
             return False
         w = norm.give_up_weight()
         self.w_gate_up = (self.w_gate_up.float() * w.to(self.w_gate_up.device)[None, :]).to(torch.bfloat16).contiguous()
@@ -64,14 +71,18 @@ class SwiGLU:
         T = h.shape[0]
         ws = ctx.workspace
         mid = ws.buffer("ffn.mid", (T, self.inter), self.dtype)
-        if not kernels.gate_up_fused(h, self.w_gate_up, mid, self.block):
+        if self.limit or not kernels.gate_up_fused(h, self.w_gate_up, mid, self.block):
             gu = ws.buffer("ffn.gate_up", (T, 2 * self.inter), self.dtype)
             kernels.linear(h, self.w_gate_up, gu)
-            kernels.swiglu(gu, mid, self.block)
+            kernels.swiglu(gu, mid, self.block, self.limit, self.alpha)
         kernels.linear(mid, self.w_down, residual32, accumulate=True)
 
     def forward_from_stream(self, x32: torch.Tensor, norm, ctx, residual32: torch.Tensor) -> None:
         """The same with the block's norm folded into the gate/up product."""
+        if self.limit:                 # the fused epilogues know the plain SiLU gate only
+            h = ctx.workspace.buffer("fused.normed", tuple(x32.shape), self.dtype)
+            norm.forward(x32, h)
+            return self.forward(h, ctx, residual32)
         mid = ctx.workspace.buffer("ffn.mid", (x32.shape[0], self.inter), self.dtype)
         normed_linear(x32, norm, self.w_gate_up, mid, ctx, gate_block=self.block)
         kernels.linear(mid, self.w_down, residual32, accumulate=True)
@@ -154,7 +165,9 @@ class RoutedExperts:
     vector that steers the choice and nothing else; optional) are chosen; a chosen expert's weight is
     its score as it is (``renormalise``: divided by the chosen scores' sum).  The last ``n_identity``
     router outputs stand for experts without matrices whose output is their input.  The result is
-    the weighted sum of the chosen experts' outputs, added in the order of the choice.
+    the weighted sum of the chosen experts' outputs, added in the order of the choice.  ``scale``: every
+    weight times that constant.  ``shared``: the spec of one more feed-forward (any registered kind)
+    that runs for every token and is added.
 
     A step groups its (token, choice) pairs by expert on the device (``moe_plan``) and runs one
     grouped product for gate and up with the activation in its epilogue and one for down; nothing
@@ -174,6 +187,9 @@ class RoutedExperts:
         self.names = dict(spec["names"])
         self.w_router = self.correction = self.w_gate_up = self.w_down = None
         self.blocked = False
+        self.scale = float(spec.get("scale") if spec.get("scale") is not None else 1.0)
+        shared = spec.get("shared")
+        self.shared = feed_forward_class(shared)(shared, hidden_size, dtype, device) if shared is not None else None
 
     @classmethod
     def expected(cls, spec: PartSpec, hidden_size: int) -> dict:
@@ -186,10 +202,14 @@ class RoutedExperts:
             out[n["gate"].format(e)] = Expected((inter, hidden_size))
             out[n["up"].format(e)] = Expected((inter, hidden_size))
             out[n["down"].format(e)] = Expected((hidden_size, inter))
+        if spec.get("shared") is not None:
+            out.update(feed_forward_class(spec["shared"]).expected(spec["shared"], hidden_size))
         return out
 
     def bind(self, tensors: dict) -> None:
         n = self.names
+        if self.shared is not None:
+            self.shared.bind(tensors)
         self.w_router = tensors[n["router"]].contiguous()
         if self.has_correction:
             self.correction = tensors[n["correction"]].to(torch.float32).contiguous()
@@ -210,7 +230,8 @@ class RoutedExperts:
             self.w_down = torch.stack([tensors[n["down"].format(e)].to(common) for e in range(self.E)]).contiguous()
 
     def weights(self):
-        return tuple(t for t in (self.w_router, self.correction, self.w_gate_up, self.w_down) if t is not None)
+        own = tuple(t for t in (self.w_router, self.correction, self.w_gate_up, self.w_down) if t is not None)
+        return own + (tuple(self.shared.weights()) if self.shared is not None else ())
 
     def notices(self) -> list:
         if self.w_gate_up is not None and self.dtype == torch.bfloat16 and \
@@ -220,9 +241,13 @@ class RoutedExperts:
         return []
 
     def forward(self, h: torch.Tensor, ctx, residual32: torch.Tensor, x_self32: torch.Tensor = None) -> None:
-        y = ctx.workspace.buffer("moe.sum", tuple(residual32.shape), torch.float32)
-        self.forward_into(h, ctx, y, x_self32)
-        residual32.add_(y)
+        rows32, pair_row, weight = self._experts(h, ctx)
+        if x_self32 is None and self.I:
+            x_self32 = h if h.dtype == torch.float32 else h.float()
+        kernels.moe_combine(rows32, pair_row, weight, x_self32 if self.I else rows32, self.top, residual32,
+                            accumulate=True)
+        if self.shared is not None:
+            self.shared.forward(h, ctx, residual32)
 
     def forward_into(self, h: torch.Tensor, ctx, out32: torch.Tensor, x_self32: torch.Tensor = None) -> None:
         """Stores the result.  ``x_self32``: the input in 32-bit, for the experts whose output is their
@@ -231,12 +256,14 @@ class RoutedExperts:
         if x_self32 is None:
             x_self32 = h if h.dtype == torch.float32 else h.float()
         kernels.moe_combine(rows32, pair_row, weight, x_self32, self.top, out32)
+        if self.shared is not None:
+            self.shared.forward(h, ctx, out32)
 
     def forward_join(self, h: torch.Tensor, ctx, x32: torch.Tensor, norm_w, eps: float, cast_out) -> bool:
         """For a block that norms the feed-forward's output before it joins the stream ``x32`` (which is
         also the feed-forward's input in 32-bit): x += sum / sqrt(mean(sum^2) + eps) * norm_w in the
         pass that sums the experts.  False (nothing done) when the width is beyond that kernel."""
-        if x32.shape[1] > 4096:
+        if x32.shape[1] > 4096 or self.shared is not None:
             return False
         rows32, pair_row, weight = self._experts(h, ctx)
         return kernels.moe_combine_norm_add(rows32, pair_row, weight, x32, norm_w, eps, self.top, cast_out)
@@ -248,7 +275,7 @@ class RoutedExperts:
         kernels.linear(h, self.w_router, z)
         idx = ws.buffer("moe.idx", (T, top), torch.int32)
         weight = ws.buffer("moe.weight", (T, top), torch.float32)
-        kernels.moe_route(z, self.correction, top, self.renormalise, idx, weight)
+        kernels.moe_route(z, self.correction, top, self.renormalise, idx, weight, self.scale)
         n_pairs = T * top
         tile = kernels.moe_tile_rows()
         max_tiles = -(-n_pairs // tile) + E               # every expert's last tile may be part full

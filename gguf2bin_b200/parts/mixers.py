@@ -21,8 +21,16 @@ position 0 of the sequence;
 ``sink`` = "zero": one more term exp(0) in the softmax's denominator, with no value;
 ``out_gate`` = "sigmoid": the concatenated heads times sigmoid(W_g h), element by element (name
 ``gate``), before the output projection;
-``out_scale``: the mixer's result times a constant (applied to the gated heads in 32-bit).
-The first, second, third and sixth take the prologue kernel that knows them
+``out_scale``: the mixer's result times a constant (applied to the gated heads in 32-bit);
+``v_norm_eps``: every value head is divided by its root mean square (that eps inside the root, no
+weight) before it is stored;
+``pool`` (with a window): beside the window's tokens a query at position i sees one key and one value
+for every block of ``pool`` positions that lies wholly before the window (block b, positions
+b pool .. b pool + pool - 1, if b pool + pool - 1 <= i - window): the means of the block's keys and
+values as the pages hold them, in the same softmax.  Tokens that have left the window and whose
+block is not complete behind it are not seen.  The means are a second store beside the pages
+(``KVNeed.rows``: a page keeps the blocks that start in it), written by the token that ends a block.
+The first, second, third, sixth and the value norm take the prologue kernel that knows them
 (``proj_norm_rope_cache``); its rotation is either pair layout of the position part.
 """
 from __future__ import annotations
@@ -80,11 +88,16 @@ class GQAAttention:
                               "'sigmoid', sink None or 'zero'")
         if self.chunk < 0 or (self.chunk and self.window):
             raise ConfigError("gqa_attention: a chunk and a window exclude each other")
+        self.v_norm_eps = float(spec.get("v_norm_eps") or 0.0)
+        self.pool = int(spec.get("pool") or 0)
+        if self.pool < 0 or (self.pool and (self.window <= 0 or sink is not None or self.out_gate)):
+            raise ConfigError("gqa_attention: pooled blocks need a window and go with neither a sink nor a gate")
         self.sink = torch.zeros(self.nh, dtype=torch.float32, device=device) if sink == "zero" else None
         self.bias = None
         # the prologue that knows biases, a norm over the whole projection, unequal head sizes and
         # a gate's columns beside q, k and v
-        self.wide = bool(self.has_bias or self.vd != self.hd or self.out_gate
+        self.wide = bool(self.has_bias or self.vd != self.hd or self.out_gate or self.v_norm_eps or self.pool
+                         or getattr(self.position, "mult", 1.0) != 1.0
                          or (self.has_qk_norm and self.norm_span == "projection"))
         if self.wide:
             if self.shared_kv or (self.has_qk_norm and self.norm_span == "head"):
@@ -161,7 +174,13 @@ class GQAAttention:
 
     # ---- cache ---------------------------------------------------------------
     def cache_need(self):
-        return None if self.shared_kv else KVNeed(self.nkv, self.cache_hd, self.window)
+        if self.shared_kv:
+            return None
+        need = KVNeed(self.nkv, self.cache_hd, self.window)
+        if not self.pool:
+            return need
+        from ..cache.storage import PAGE_SIZE
+        return {"kv": need, "pool": KVNeed(self.nkv, self.cache_hd, 0, rows=-(-PAGE_SIZE // self.pool))}
 
     # ---- step ----------------------------------------------------------------
     def forward(self, h: torch.Tensor, ctx, view: KVView, residual32: torch.Tensor) -> None:
@@ -187,15 +206,20 @@ class GQAAttention:
         of q and all of k, rotates and writes the pages; attention; gate; output product."""
         T, ws = qkv.shape[0], ctx.workspace
         hd, no = self.cache_hd, self.nh * self.vd
+        pooled = None
+        if self.pool:
+            view, pooled = view["kv"], view["pool"].pages
         inv_freq, rot, interleaved = self.position.table_rotation()
-        rope = ctx.rope_table(inv_freq) if inv_freq is not None else None
+        rope = ctx.rope_table(inv_freq, getattr(self.position, "mult", 1.0)) if inv_freq is not None else None
         q = ws.buffer("attn.q", (T, self.nh * hd), self.dtype)
         kernels.proj_norm_rope_cache(qkv, self.bias, self.nh, self.nkv, self.hd, self.vd, self.q_norm_w,
                                      self.k_norm_w, self.qk_eps, rope, rot, interleaved, ctx, view.pages,
-                                     view.page_size, q)
+                                     view.page_size, q, v_norm_eps=self.v_norm_eps)
+        if self.pool:
+            kernels.pool_update(view.pages, pooled, ctx, self.nkv, hd, view.page_size, self.pool)
         o = ws.buffer("attn.o", (T, self.nh * hd), self.dtype)
         kernels.attention(q, o, view.pages, ctx, self.nh, self.nkv, hd, view.page_size, self.window,
-                          self.scale, sink=self.sink, chunk=self.chunk)
+                          self.scale, sink=self.sink, chunk=self.chunk, pooled=pooled, pool=self.pool)
         if self.out_gate or hd != self.vd or self.out_scale != 1.0:
             gate = qkv[:, qkv.shape[1] - no:] if self.out_gate else None
             og = ws.buffer("attn.gated", (T, no), self.dtype)

@@ -8,6 +8,12 @@ changes the frequencies needs no kernel of its own.
 ``rope_interleaved``: the same angles on neighbouring pairs (2j, 2j + 1).  No fused kernel takes
 that layout, so a mixer runs it as a step of its own (``apply``) or hands ``table_rotation()`` to
 a kernel that knows both layouts.
+``rope_stretched``: the half-split rotation with its slow pairs slowed further, for sequences
+longer than the ``original`` length: with pair(t) = r ln(original / (2 pi t)) / (2 ln theta) the pair
+index that makes t turns over ``original`` positions, lo = max(floor(pair(fast)), 0),
+hi = min(ceil(pair(slow)), r - 1) and ramp_j = clamp((j - lo) / max(hi - lo, 0.001), 0, 1), pair j
+turns at f_j (1 - ramp_j) + (f_j / factor) ramp_j, and cos and sin are both multiplied by
+0.1 ln(factor) + 1 (``mult``; the step's table carries it).
 ``none``: nothing is applied.
 """
 from __future__ import annotations
@@ -40,6 +46,7 @@ class RopeNeox:
         self.inv_freq = _INV_FREQ[key]
 
     interleaved = False
+    mult = 1.0                 # what cos and sin are multiplied by (the step's table carries it)
 
     def fused_rotation(self):
         return self.inv_freq, self.rotary_dim
@@ -64,6 +71,42 @@ class RopeNeox:
                                       0.0, rope, self.rotary_dim, ctx.tok_pos, ctx.tok_seq, None,
                                       None, ctx.page_size, out)
             a.copy_(out)
+
+
+class RopeStretched(RopeNeox):
+    """Half-split pairs whose frequencies are divided by ``factor`` along a ramp over the pair index."""
+
+    def __init__(self, spec: PartSpec, head_dim: int, device):
+        super().__init__(spec, head_dim, device)
+        factor, original = float(spec["factor"]), float(spec["original"])
+        fast, slow = float(spec["fast"]), float(spec["slow"])
+        if not (factor > 0 and original > 0 and fast > 0 and slow > 0 and self.theta > 1.0):
+            raise ConfigError("rope_stretched: factor, original, fast and slow must be positive, theta above 1")
+        key = (self.theta, self.rotary_dim, str(device), factor, original, fast, slow)
+        if key not in _INV_FREQ:
+            import math
+            r = self.rotary_dim
+
+            def pair(turns):
+                return r * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.theta))
+            lo, hi = max(math.floor(pair(fast)), 0), min(math.ceil(pair(slow)), r - 1)
+            j = torch.arange(r // 2, dtype=torch.float64)
+            f = self.theta ** (-2.0 * j / r)
+            ramp = ((j - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+            _INV_FREQ[key] = (f / factor * ramp + f * (1.0 - ramp)).to(torch.float32).to(device)
+        self.inv_freq = _INV_FREQ[key]
+        import math
+        self.mult = 0.1 * math.log(factor) + 1.0
+
+    def fused_rotation(self):
+        return None if self.mult != 1.0 else (self.inv_freq, self.rotary_dim)     # the fused kernel's table has no factor
+
+    def apply(self, q, k, ctx) -> None:
+        from .. import kernels
+        rope = ctx.rope_table(self.inv_freq, self.mult)
+        for a in (q, k):
+            if a is not None and a.numel():
+                kernels.rotate_heads(a, a.shape[1] // self.head_dim, self.head_dim, rope, self.rotary_dim, False)
 
 
 class RopeInterleaved(RopeNeox):
@@ -99,4 +142,5 @@ class NoPosition:
 
 register_position("rope_neox", RopeNeox)
 register_position("rope_interleaved", RopeInterleaved)
+register_position("rope_stretched", RopeStretched)
 register_position("none", NoPosition)

@@ -14,6 +14,21 @@ b = sigmoid(W_b h), g = exp(-exp(A_log) softplus(W_a h + dt_bias)); then S <- g 
 u = b (v - S^T k); S <- S + k u^T; o = S^T q, in this order.  Each head's o divided by its root mean
 square, times a weight over v_dim shared by the heads, times silu(W_g h); output product.
 
+``ssd``: a state-space mixer with one scalar decay per head and token (the state-space duality form).
+One input product laid out as [z: inner | x: inner | B: groups*state | C: groups*state | dt: heads],
+inner = heads * v_dim; x, B and C together pass a causal convolution per channel (``conv_taps`` taps,
+the last the current token's, with a bias) and SiLU; dt = softplus(dt + dt_bias); per head (head h
+reads group h // (heads / groups)) S = exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x; y times
+silu(z), THEN divided by its root mean square in ``norm_groups`` equal parts, times a weight; output
+product.  In the scan's words: q = C, k = B, v = x, decay and strength per token from ``scan_gates_step``.
+
+``mlstm``: a matrix memory with exponential gates.  q = W_q h * qk_dim^-1/2, k = W_k h, v = W_v h; per
+head and token a log input gate i = cap tanh((W_i h + b_i) / cap) and a log forget gate
+f = logsigmoid(cap tanh((W_f h + b_f) / cap)); with a running maximum m (from 0): m' = max(f + m, i),
+S = exp(f + m - m') S + exp(i - m') k v^T, n likewise with k alone, o = S^T q / (max(|n . q|, exp(-m')) + 1e-6);
+each head's o divided by its root mean square, times a weight over all heads, times sigmoid(W_g h);
+output product.  n rides in the scan as one more column of S whose value is always 1.
+
 ``parallel``: several mixers that read the same input; the result is the sum of theirs, each times
 its ``out_scale``.  A branch is any registered mixer that takes ``out_scale``.
 
@@ -194,6 +209,179 @@ class GatedDeltaMixer:
         kernels.linear(og, self.w_o, residual32, accumulate=accumulate)
 
 
+def _padded_rows(parts, multiple: int = 8):
+    """The matrices one under the other in a common type, with rows of zeros up to a multiple
+    (an output row then starts on 16 bytes in bfloat16)."""
+    common = _common_dtype(parts)
+    rows = sum(p.shape[0] for p in parts)
+    pad = -rows % multiple
+    mats = [p.to(common) for p in parts]
+    if pad:
+        mats.append(torch.zeros((pad, parts[0].shape[1]), dtype=common, device=parts[0].device))
+    return torch.cat(mats, dim=0).contiguous()
+
+
+class SSDMixer:
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, hidden_size: int, dtype: torch.dtype, device):
+        self.H, self.G = int(spec["n_heads"]), int(spec["n_groups"])
+        self.N, self.V = int(spec["state_dim"]), int(spec["v_dim"])
+        self.taps, self.norm_groups = int(spec["conv_taps"]), int(spec.get("norm_groups") or 1)
+        self.hidden, self.dtype, self.device = int(hidden_size), dtype, device
+        if self.G <= 0 or self.H % self.G:
+            raise ConfigError(f"ssd: {self.H} heads are not a multiple of {self.G} groups")
+        if min(self.N, self.V) <= 0 or self.N > 512 or not (1 <= self.taps <= 16):
+            raise ConfigError("ssd: state_dim in 1..512, v_dim positive, conv_taps in 1..16")
+        if self.norm_groups <= 0 or self.inner % self.norm_groups:
+            raise ConfigError(f"ssd: {self.norm_groups} norm groups do not divide {self.inner} channels")
+        self.eps = float(spec["eps"])
+        self.names = dict(spec["names"])
+        self.w_in = self.w_conv = self.b_conv = self.a_log = self.dt_bias = self.skip = self.norm_w = self.w_o = None
+
+    @property
+    def inner(self) -> int:
+        return self.H * self.V
+
+    @property
+    def channels(self) -> int:
+        return self.inner + 2 * self.G * self.N
+
+    @classmethod
+    def expected(cls, spec: PartSpec, hidden_size: int) -> dict:
+        n = dict(spec["names"])
+        H, G, N, V, taps = (int(spec[k]) for k in ("n_heads", "n_groups", "state_dim", "v_dim", "conv_taps"))
+        inner, C = H * V, H * V + 2 * G * N
+        return {n["in"]: Expected((2 * inner + 2 * G * N + H, hidden_size)), n["conv"]: Expected((C, taps)),
+                n["conv_bias"]: Expected((C,)), n["dt_bias"]: Expected((H,)), n["a_log"]: Expected((H,)),
+                n["skip"]: Expected((H,)), n["norm"]: Expected((inner,), init="scale"),
+                n["o"]: Expected((hidden_size, inner))}
+
+    def bind(self, tensors: dict) -> None:
+        n = self.names
+        self.w_in = _padded_rows([tensors[n["in"]]])             # z | x | B | C | dt (| zeros)
+        self.w_conv = tensors[n["conv"]].to(torch.float32).t().contiguous()          # [taps, channels]
+        self.b_conv = tensors[n["conv_bias"]].to(torch.float32).contiguous()
+        self.a_log = tensors[n["a_log"]].to(torch.float32).contiguous()
+        self.dt_bias = tensors[n["dt_bias"]].to(torch.float32).contiguous()
+        self.skip = tensors[n["skip"]].to(torch.float32).contiguous()
+        self.norm_w = tensors[n["norm"]].to(torch.float32).contiguous()
+        self.w_o = tensors[n["o"]].contiguous()
+
+    def weights(self):
+        return (self.w_in, self.w_conv, self.b_conv, self.a_log, self.dt_bias, self.skip, self.norm_w, self.w_o)
+
+    def notices(self) -> list:
+        return (kernels.product_notices("state-space input", self.w_in, self.dtype)
+                + kernels.product_notices("state-space output", self.w_o, self.dtype))
+
+    def cache_need(self):
+        need = {"state": StateNeed((self.H, self.V, self.N), torch.float32)}
+        if self.taps > 1:
+            need["conv"] = StateNeed((self.taps, self.channels), self.dtype, by_position=True)
+        return need
+
+    def forward(self, h: torch.Tensor, ctx, view, residual32: torch.Tensor) -> None:
+        self._run(h, ctx, view, residual32, True)
+
+    def forward_store(self, h: torch.Tensor, ctx, view, out32: torch.Tensor) -> None:
+        """Stores the result instead of adding it."""
+        self._run(h, ctx, view, out32, False)
+
+    def _run(self, h, ctx, view, residual32, accumulate: bool) -> None:
+        T, ws = h.shape[0], ctx.workspace
+        inner, C, gn = self.inner, self.channels, self.G * self.N
+        proj = ws.buffer("ssd.in", (T, self.w_in.shape[0]), self.dtype)
+        kernels.linear(h, self.w_in, proj)
+        mixed = ws.buffer("ssd.conv", (T, C), self.dtype)
+        ring = view["conv"].states if self.taps > 1 else None
+        kernels.short_conv(proj[:, inner:inner + C], self.w_conv, ring, ctx, mixed, act=True, bias=self.b_conv)
+        gates = ws.buffer("ssd.gates", (T, 2 * self.H), torch.float32)
+        kernels.scan_gates_step(proj[:, inner + C:inner + C + self.H], self.a_log, self.dt_bias, gates)
+        o32 = ws.buffer("ssd.o", (T, inner), torch.float32)
+        kernels.state_scan(mixed[:, inner + gn:], mixed[:, inner:inner + gn], mixed[:, :inner], view["state"].states,
+                           ctx, o32, self.H, self.G, self.N, self.V, gates=gates)
+        og = ws.buffer("ssd.gated", (T, inner), self.dtype)
+        kernels.state_readout(o32, self.H, self.V, og, skip_x=mixed[:, :inner], skip_w=self.skip, gate=proj[:, :inner],
+                              gate_act="silu", gate_first=True, group=inner // self.norm_groups, eps=self.eps,
+                              w=self.norm_w)
+        kernels.linear(og, self.w_o, residual32, accumulate=accumulate)
+
+
+class MLSTMMixer:
+    graph_safe = True
+    DEN_EPS = 1e-6            # added to the read-out's denominator
+
+    def __init__(self, spec: PartSpec, hidden_size: int, dtype: torch.dtype, device):
+        self.H, self.D, self.V = int(spec["n_heads"]), int(spec["qk_dim"]), int(spec["v_dim"])
+        self.cap = float(spec["gate_cap"])
+        self.hidden, self.dtype, self.device = int(hidden_size), dtype, device
+        if min(self.H, self.D, self.V) <= 0 or self.D > 512:
+            raise ConfigError("mlstm: heads, qk_dim (at most 512) and v_dim must be positive")
+        if not self.cap > 0:
+            raise ConfigError("mlstm: gate_cap must be positive")
+        self.eps = float(spec["eps"])
+        self.names = dict(spec["names"])
+        self.w_in = self.w_o = self.b_i = self.b_f = self.norm_w = None
+
+    @classmethod
+    def expected(cls, spec: PartSpec, hidden_size: int) -> dict:
+        n = dict(spec["names"])
+        H, D, V = int(spec["n_heads"]), int(spec["qk_dim"]), int(spec["v_dim"])
+        return {n["q"]: Expected((H * D, hidden_size)), n["k"]: Expected((H * D, hidden_size)),
+                n["v"]: Expected((H * V, hidden_size)), n["gate"]: Expected((H * V, hidden_size)),
+                n["i"]: Expected((H, hidden_size)), n["i_bias"]: Expected((H,)),
+                n["f"]: Expected((H, hidden_size)), n["f_bias"]: Expected((H,)),
+                n["norm"]: Expected((H * V,), init="scale"), n["o"]: Expected((hidden_size, H * V))}
+
+    def bind(self, tensors: dict) -> None:
+        n = self.names
+        # one product: q | k | v | gate | i | f (| zeros)
+        self.w_in = _padded_rows([tensors[n[k]] for k in ("q", "k", "v", "gate", "i", "f")])
+        self.b_i = tensors[n["i_bias"]].to(torch.float32).contiguous()
+        self.b_f = tensors[n["f_bias"]].to(torch.float32).contiguous()
+        self.norm_w = tensors[n["norm"]].to(torch.float32).contiguous()
+        self.w_o = tensors[n["o"]].contiguous()
+
+    def weights(self):
+        return (self.w_in, self.b_i, self.b_f, self.norm_w, self.w_o)
+
+    def notices(self) -> list:
+        return (kernels.product_notices("mlstm input", self.w_in, self.dtype)
+                + kernels.product_notices("mlstm output", self.w_o, self.dtype))
+
+    def cache_need(self):
+        # S with the normaliser as its last column, and the running maximum
+        return {"state": StateNeed((self.H, self.V + 1, self.D), torch.float32),
+                "max": StateNeed((self.H,), torch.float32)}
+
+    def forward(self, h: torch.Tensor, ctx, view, residual32: torch.Tensor) -> None:
+        self._run(h, ctx, view, residual32, True)
+
+    def forward_store(self, h: torch.Tensor, ctx, view, out32: torch.Tensor) -> None:
+        """Stores the result instead of adding it."""
+        self._run(h, ctx, view, out32, False)
+
+    def _run(self, h, ctx, view, residual32, accumulate: bool) -> None:
+        T, ws = h.shape[0], ctx.workspace
+        H, nq, nv = self.H, self.H * self.D, self.H * self.V
+        proj = ws.buffer("mlstm.in", (T, self.w_in.shape[0]), self.dtype)
+        kernels.linear(h, self.w_in, proj)
+        at = 2 * nq + 2 * nv
+        gates = ws.buffer("mlstm.gates", (T, 2 * H), torch.float32)
+        m = ws.buffer("mlstm.max", (T, H), torch.float32)
+        kernels.scan_gates_max(proj[:, at:at + H], proj[:, at + H:at + 2 * H], self.b_i, self.b_f, self.cap,
+                               view["max"].states, ctx, gates, m)
+        o32 = ws.buffer("mlstm.o", (T, H * (self.V + 1)), torch.float32)
+        kernels.state_scan(proj[:, :nq], proj[:, nq:2 * nq], proj[:, 2 * nq:2 * nq + nv], view["state"].states, ctx,
+                           o32, H, H, self.D, self.V, gates=gates, q_scale=self.D ** -0.5, ones_column=True)
+        og = ws.buffer("mlstm.gated", (T, nv), self.dtype)
+        kernels.state_readout(o32, H, self.V, og, stored_cols=self.V + 1, m=m, den_eps=self.DEN_EPS,
+                              gate=proj[:, 2 * nq + nv:at], gate_act="sigmoid", gate_first=False, group=self.V,
+                              eps=self.eps, w=self.norm_w)
+        kernels.linear(og, self.w_o, residual32, accumulate=accumulate)
+
+
 class ParallelMixer:
     """Branches side by side on one input; what each stores is kept under ``<branch>.<name>``."""
 
@@ -259,3 +447,5 @@ class ParallelMixer:
 register_mixer("retention", RetentionMixer)
 register_mixer("gated_delta", GatedDeltaMixer)
 register_mixer("parallel", ParallelMixer)
+register_mixer("ssd", SSDMixer)
+register_mixer("mlstm", MLSTMMixer)
