@@ -112,20 +112,21 @@ def window_pool_attention(q, k, v, scale, window, pool, round_cache=None):
     keep = round_cache or (lambda a: a)
     k, v = keep(k), keep(v)
     out = np.zeros((T, H, V))
+    whole = T // pool if pool > 0 else 0
+    if whole:
+        mk = keep(np.stack([k[b * pool:(b + 1) * pool].mean(axis=0) for b in range(whole)]))      # [blocks, G, D]
+        mv = keep(np.stack([v[b * pool:(b + 1) * pool].mean(axis=0) for b in range(whole)]))
     for i in range(T):
         lo = max(0, i - window + 1)
         n_blocks = max(0, (i - window + 1) // pool) if pool > 0 else 0
         for h in range(H):
             g = h // (H // G)
-            keys = [k[j, g] for j in range(lo, i + 1)]
-            vals = [v[j, g] for j in range(lo, i + 1)]
-            for b in range(n_blocks):
-                keys.append(keep(k[b * pool:(b + 1) * pool, g].mean(axis=0)))
-                vals.append(keep(v[b * pool:(b + 1) * pool, g].mean(axis=0)))
-            s = np.array([q[i, h] @ kk for kk in keys]) * scale
+            keys, vals = k[lo:i + 1, g], v[lo:i + 1, g]
+            if n_blocks:
+                keys, vals = np.vstack([keys, mk[:n_blocks, g]]), np.vstack([vals, mv[:n_blocks, g]])
+            s = (keys @ q[i, h]) * scale
             p = np.exp(s - s.max())
-            p /= p.sum()
-            out[i, h] = sum(pj * vj for pj, vj in zip(p, vals))
+            out[i, h] = (p / p.sum()) @ vals
     return out
 
 
