@@ -2,7 +2,7 @@
 """Decode and prefill throughput of gguf2bin_b200 on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload decode|ragged8|b64|senotar|levolix] [--batch B] [--layers L] [--context C]
+                    [--workload decode|ragged8|b64|senotar|levolix|sominex] [--batch B] [--layers L] [--context C]
                     [--no-points] [--sizes 0.6b|8b|14b]
 
 The default run has the layer sizes of Qwen3-0.6B (28 layers, width 1024, 16/8 heads of
@@ -451,6 +451,129 @@ def levolix_comparison(a, pk) -> int:
     return 0
 
 
+# ---- Sominex beside Qwen3 at equal sizes ----------------------------------------------------------
+# name: (width, attention heads / kv heads / head size / window / block, state-space heads / groups / state / value size,
+#        mLSTM heads / key size / value size, dense ff, experts / top / expert ff / shared ff;
+#        Qwen3's heads, kv heads, head size, ff)
+SOMINEX_SIZES = {
+    "w1024": (1024, (8, 4, 128, 512, 64), (32, 4, 128, 64), (4, 128, 256), 3072, (16, 2, 768, 1536), 16, 8, 128, 3072),
+    "w2048": (2048, (16, 8, 128, 512, 64), (64, 8, 128, 64), (8, 128, 256), 6144, (16, 2, 1536, 3072), 16, 8, 128, 6144),
+    "w4096": (4096, (32, 8, 128, 512, 64), (128, 8, 128, 64), (16, 128, 256), 12288, (16, 2, 3072, 6144), 32, 8, 128, 12288),
+}
+
+
+def sominex_config(width, att, ssm, mls, ff, moe, layers, vocab) -> dict:
+    """Attention, state space, mLSTM in turn; dense and routed feed-forwards in turn."""
+    out = []
+    dense = dict(kind="dense", ff=ff, limit=7.0)
+    routed = dict(kind="moe", expert=dict(ff=moe[2]), router=dict(experts=moe[0], top=moe[1], scale=2.5), shared=dict(ff=moe[3]))
+    for i in range(layers):
+        mlp = routed if i % 2 else dense
+        if i % 3 == 0:
+            H, G, D, window, pool = att
+            scaling = dict(factor=4.0, original=2048, fast=32.0, slow=1.0)
+            out.append(dict(type="attention", mlp=mlp,
+                            mixer=dict(heads=H, kv_heads=G, dim=D, vdim=D, scale=D ** -0.5, mask=dict(size=window, pool=pool),
+                                       rot=dict(dims=D // 2, base=1e6, scaling=scaling))))
+        elif i % 3 == 1:
+            H, G, N, V = ssm
+            out.append(dict(type="mamba2", mlp=mlp, mixer=dict(heads=H, groups=G, state=N, vdim=V, conv=4, norm_groups=G)))
+        else:
+            H, D, V = mls
+            out.append(dict(type="mlstm", mlp=mlp, mixer=dict(heads=H, dim=D, vdim=V, gate_cap=15.0)))
+    return dict(architecture="Sominex", width=width, vocab=vocab, norm=dict(eps=1e-5), embedding=dict(scale=1.0), layers=out)
+
+
+def sominex_bytes_and_flops(cfg: dict, T: int) -> dict:
+    """Parameters a token's step multiplies by (the chosen experts and the shared one), the bytes a decode
+    step of a batch reads at least (every matrix once, every state read and written, the window's keys
+    and the blocks' means in front of it), and the (query, key) pairs of a prompt of T tokens."""
+    W, V = cfg["width"], cfg["vocab"]
+    active = total = state_bytes = 0
+    attn_layers = []
+    pair_flops = 0.0
+    for layer in cfg["layers"]:
+        m, mlp = layer["mixer"], layer["mlp"]
+        if layer["type"] == "attention":
+            mix = W * (2 * m["heads"] * m["dim"] + 2 * m["kv_heads"] * m["dim"])
+            attn_layers.append((2 * 2 * m["kv_heads"] * m["dim"], m["mask"]["size"], m["mask"]["pool"]))
+            pairs = sum(min(t + 1, m["mask"]["size"]) + max(0, (t - m["mask"]["size"] + 1) // m["mask"]["pool"]) for t in range(T))
+            pair_flops += 4.0 * m["heads"] * m["dim"] * pairs
+        elif layer["type"] == "mamba2":
+            inner = m["heads"] * m["vdim"]
+            mix = W * (3 * inner + 2 * m["groups"] * m["state"] + m["heads"])
+            state_bytes += 2 * 4 * m["heads"] * m["state"] * m["vdim"]
+        else:
+            mix = W * m["heads"] * (2 * m["dim"] + 3 * m["vdim"] + 2)
+            state_bytes += 2 * 4 * m["heads"] * m["dim"] * (m["vdim"] + 1)
+        if mlp["kind"] == "dense":
+            a = t = 3 * W * mlp["ff"]
+        else:
+            r = mlp["router"]
+            a = W * r["experts"] + 3 * W * (mlp["expert"]["ff"] * r["top"] + mlp["shared"]["ff"])
+            t = W * r["experts"] + 3 * W * (mlp["expert"]["ff"] * r["experts"] + mlp["shared"]["ff"])
+        active += mix + a
+        total += mix + t
+
+    def kv_bytes(ctx: float) -> float:
+        return sum(b * (min(ctx, w) + max(0.0, ctx - w) / p) for b, w, p in attn_layers)
+    return dict(layer_params=active, total_params=total, weight_bytes=2 * (total + 2 * V * W), state_bytes=state_bytes,
+                kv_bytes=kv_bytes, pair_flops=pair_flops)
+
+
+def sominex_comparison(a, pk) -> int:
+    import torch
+    from gguf2bin_b200.api import LLM
+    layers, vocab, batch, T = a.layers or 6, 151936, a.batch or 8, a.prefill_tokens
+    steps, warmup = a.steps or 128, max(a.warmup, 8)
+    max_tokens = batch * (T + warmup + steps + 128)
+    rows = {}
+    clocks = ClockSampler()
+    clocks.start()
+    for name, (width, att, ssm, mls, ff, moe, q_heads, q_kv, q_hd, q_ff) in SOMINEX_SIZES.items():
+        if a.sizes_only and name not in a.sizes_only.split(","):
+            continue
+        row = {}
+        for arch in ("sominex", "qwen3"):
+            if arch == "sominex":
+                cfg = sominex_config(width, att, ssm, mls, ff, moe, layers, vocab)
+                sizes = sominex_bytes_and_flops(cfg, T)
+                flops = 2.0 * T * sizes["layer_params"] + sizes["pair_flops"] + 2.0 * vocab * width
+            else:
+                cfg = dict(QWEN3_0P6B, hidden_size=width, intermediate_size=q_ff, num_hidden_layers=layers,
+                           num_attention_heads=q_heads, num_key_value_heads=q_kv, head_dim=q_hd, vocab_size=vocab,
+                           tie_word_embeddings=False)
+                sizes = model_bytes_and_flops(cfg, layers)
+                sizes["layer_params"] *= layers
+                flops = prefill_flops(cfg, layers, [T])
+            llm = LLM.random(cfg, seed=0, dtype="bfloat16", max_tokens=max_tokens, max_seqs=batch + 1)
+            first, ms, plain = timed_prompt_step(llm, random_prompts(1, T, vocab, 1), repeats=3)
+            sec, per_step, mean_ctx = decode_device_timed(llm, random_prompts(batch, T, vocab, 100), steps, warmup,
+                                                          vocab, whole_batch_prefill=False)
+            if arch == "sominex":
+                step_bytes = sizes["weight_bytes"] + batch * (sizes["state_bytes"] + sizes["kv_bytes"](mean_ctx))
+            else:
+                step_bytes = sizes["weight_bytes"] + batch * mean_ctx * sizes["kv_bytes_per_token"]
+            gbs = step_bytes / (sec / steps) / 1e9
+            row[arch] = dict(
+                active_parameters_per_layer_m=round(sizes["layer_params"] / layers / 1e6, 1),
+                prefill_tokens_per_s=round(T / (ms / 1e3)), prefill_ms=round(ms, 3), prefill_plain_ms=round(plain, 3),
+                prefill_frac_of_tensor_peak=round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 3),
+                decode_tokens_per_s=round(batch * steps / sec), decode_ms_per_step=round(sec / steps * 1e3, 4),
+                decode_launches_per_step=per_step, decode_step_mb=round(step_bytes / 1e6, 1), decode_gbs=round(gbs),
+                decode_frac_of_copy_bandwidth=round(gbs / pk["hbm_gbs"], 3))
+            del llm
+            torch.cuda.empty_cache()
+        rows[name] = row
+    print(json.dumps({"metric": "prefill and decode tokens/s of Sominex beside Qwen3 at equal sizes (random weights)",
+                      "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+                      "config": {"layers": layers, "vocab": vocab, "prompt_tokens": T, "decode_batch": batch,
+                                 "decode_context_from": T + warmup, "decode_steps": steps, "peaks": pk["source"],
+                                 "l2": "inputs larger than L2 (weights, states and cache read every step)"},
+                      "sizes": rows, "clocks": clocks.stop()}))
+    return 0
+
+
 WORKLOADS = {
     # name: (sizes, batch, what it is)
     "decode": ("0.6b", 8, "every sequence prefilled to half the context, then decoded"),
@@ -458,6 +581,7 @@ WORKLOADS = {
     "b64": ("14b", 64, "64 prompts of 512 tokens in one prompt step, decoded to a context of 2048"),
     "senotar": (None, 8, "Senotar beside Qwen3 at equal sizes: a 2,048-token prompt step and batch-8 decode steps each"),
     "levolix": (None, 8, "Levolix beside Qwen3 at equal sizes: a 2,048-token prompt step and batch-8 decode steps each"),
+    "sominex": (None, 8, "Sominex beside Qwen3 at equal sizes: a 2,048-token prompt step and batch-8 decode steps each"),
 }
 
 
@@ -478,7 +602,7 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="length of the prompt of the prefill figure (decode workload; default 2048)")
     ap.add_argument("--sizes-only", default=None,
-                    help="senotar and levolix workloads: a comma-separated subset of " + ",".join(EQUAL_SIZES))
+                    help="senotar, levolix and sominex workloads: a comma-separated subset of " + ",".join(EQUAL_SIZES))
     a = ap.parse_args()
 
     if a.impl == "reference":
@@ -496,6 +620,8 @@ def main() -> int:
         return senotar_comparison(a, peaks())
     if a.workload == "levolix":
         return levolix_comparison(a, peaks())
+    if a.workload == "sominex":
+        return sominex_comparison(a, peaks())
 
     import numpy as np
     import torch
