@@ -33,6 +33,17 @@
 // Every mbarrier wait is bounded; a wait that gives up records a code in `*status`, all roles
 // fall through to the common exit and the tensor memory is freed.
 //
+// Pooled blocks (the second instantiation, `POOLED`): with a window and `pool` > 0 a query at
+// position p also sees one key and value for every block of `pool` positions that lies wholly
+// before its window: block j if j pool + pool - 1 <= p - window.  They come from a second store
+// ([pages, 2, nkv, pool_rows, HD]; block j in the page of its first position, at row
+// j - ceil(that page's first position / pool)) and take the panels in front of the window's pages:
+// panel i holds blocks 64 i .. 64 i + 63.  No tiled copy fits rows that lie a page apart, so the
+// whole producer warp gathers such a panel with 16-byte loads into the layout that a swizzled copy
+// would have written (rows past the tile's last block are zeros), makes it visible to the tensor
+// cores' proxy and completes the same barrier.  The softmax masks block j of a row at position p
+// when j >= floor((p - window + 1) / pool); everything else is the same pipeline.
+//
 // Formula: src/l5_model.c:518, 559-577 of AnonymoDGH/gguf2bin.  -DHD=64 or 128; 64-key pages.
 #include "common.cuh"
 #include "tc_common.cuh"
@@ -117,13 +128,15 @@ __device__ unsigned long long g2b_timing[16];
 #ifndef G2B_ATTN_MINBLOCKS
 #define G2B_ATTN_MINBLOCKS 2
 #endif
+template <bool POOLED>
 __global__ void __launch_bounds__(THREADS, G2B_ATTN_MINBLOCKS)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                        const __grid_constant__ CUtensorMap map_kv, bf16 *__restrict__ out,
                        const int4 *__restrict__ tiles, const int *__restrict__ page_table, int P,
                        int nh, int nkv, int window, float scale_log2, int first_wave,
                        int *__restrict__ status, const float *__restrict__ sink, int planes,
-                       const bf16 *__restrict__ gate, int gate_stride) {
+                       const bf16 *__restrict__ gate, int gate_stride, const bf16 *__restrict__ pooled,
+                       int pool, int pool_rows) {
   pdl_launch();
   // The swizzled panels need 1024-byte alignment.  The kernel has no static shared memory, so
   // the dynamic part starts at the aligned base of the window; checked rather than assumed.
@@ -180,35 +193,81 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   const int h = item % nh, kvh = h / (nh / nkv);
   const int first_page = first_visible_key(pos0, window) / PAGE;
   const int last_page = (pos0 + n_rows - 1) / PAGE;
-  const int n_pages = last_page - first_page + 1;
+  // panels: first the pooled blocks that the tile's last row sees, 64 a panel, then the window's pages
+  const int nb_max = POOLED ? max(0, pos0 + n_rows - window) / pool : 0;
+  const int n_pp = (nb_max + PAGE - 1) / PAGE;
+  const int n_pages = n_pp + last_page - first_page + 1;
 
   if (warp == SOFTMAX_WARPS) {
-    if (lane == 0 && PRODUCER_RUNS) {
-      mbar_expect_tx(q_full, Q_BYTES);
-#pragma unroll
-      for (int sub = 0; sub < SUBS; ++sub)
-        tma_load_2d(smem_addr(q_smem + sub * Q_SUB_BYTES), &map_q, h * HD + 64 * sub, t0, q_full);
-      const int *pt = page_table + (size_t)b * P + first_page;
-      auto load_k = [&](int i) -> bool {
-        const int s = i % K_STAGES;
-        if (i >= K_STAGES && !mbar_wait(k_empty0 + 8 * s, ((i / K_STAGES) - 1) & 1)) return false;
-        const int row = ((pt[i] * planes + 0) * nkv + kvh) * PAGE;
-        const uint32_t dst = smem_addr(k_smem + s * KV_BYTES);
-        mbar_expect_tx(k_full0 + 8 * s, KV_BYTES);
+    // without pooled blocks one thread issues every copy; with them the whole warp goes through the
+    // same sequence, because it gathers the pooled panels together
+    if ((POOLED || lane == 0) && PRODUCER_RUNS) {
+      if (lane == 0) {
+        mbar_expect_tx(q_full, Q_BYTES);
 #pragma unroll
         for (int sub = 0; sub < SUBS; ++sub)
-          tma_load_2d(dst + sub * KV_SUB_BYTES, &map_kv, 64 * sub, row, k_full0 + 8 * s);
+          tma_load_2d(smem_addr(q_smem + sub * Q_SUB_BYTES), &map_q, h * HD + 64 * sub, t0, q_full);
+      }
+      const int *pt_seq = page_table + (size_t)b * P;
+      const int *pt = pt_seq + first_page;
+      // whether the stage is free again; with pooled blocks thread 0 waits and tells the others
+      auto stage_free = [&](uint32_t bar, uint32_t parity) -> bool {
+        if (!POOLED) return mbar_wait(bar, parity);
+        int ok = lane == 0 ? (int)mbar_wait(bar, parity) : 0;
+        return __shfl_sync(0xffffffffu, ok, 0) != 0;
+      };
+      // blocks 64 panel .. 64 panel + 63 of plane 0 (keys) or 1 (values) as a swizzled panel
+      auto gather = [&](unsigned char *dst, int panel, int plane, uint32_t full_bar) {
+        constexpr int PIECES = SUBS * 8;                       // 16-byte pieces of a row
+#pragma unroll 4
+        for (int it = 0; it < PAGE * PIECES / 32; ++it) {
+          const int idx = it * 32 + lane;
+          const int row = idx / PIECES, piece = idx % PIECES;
+          const int blk = PAGE * panel + row;
+          int4 v = make_int4(0, 0, 0, 0);
+          if (blk < nb_max) {
+            const int home = (blk * pool) / PAGE;
+            const int prow = blk - (home * PAGE + pool - 1) / pool;
+            const size_t page = (size_t)pt_seq[home];
+            v = __ldg(reinterpret_cast<const int4 *>(
+                pooled + (((page * 2 + plane) * nkv + kvh) * pool_rows + prow) * HD + piece * 8));
+          }
+          *reinterpret_cast<int4 *>(dst + (piece >> 3) * KV_SUB_BYTES + row * 128 + (((piece & 7) ^ (row & 7)) << 4)) = v;
+        }
+        fence_async_shared();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_bar);
+      };
+      auto load_k = [&](int i) -> bool {
+        const int s = i % K_STAGES;
+        if (i >= K_STAGES && !stage_free(k_empty0 + 8 * s, ((i / K_STAGES) - 1) & 1)) return false;
+        if (POOLED && i < n_pp) {
+          gather(k_smem + s * KV_BYTES, i, 0, k_full0 + 8 * s);
+        } else if (lane == 0) {
+          const int row = ((pt[i - n_pp] * planes + 0) * nkv + kvh) * PAGE;
+          const uint32_t dst = smem_addr(k_smem + s * KV_BYTES);
+          mbar_expect_tx(k_full0 + 8 * s, KV_BYTES);
+#pragma unroll
+          for (int sub = 0; sub < SUBS; ++sub)
+            tma_load_2d(dst + sub * KV_SUB_BYTES, &map_kv, 64 * sub, row, k_full0 + 8 * s);
+        }
+        if (POOLED) __syncwarp();
         return true;
       };
       auto load_v = [&](int i) -> bool {
         const int s = i % V_STAGES;
-        if (i >= V_STAGES && !mbar_wait(v_empty0 + 8 * s, ((i / V_STAGES) - 1) & 1)) return false;
-        const int row = ((pt[i] * planes + (planes - 1)) * nkv + kvh) * PAGE;      // one panel: it is keys and values
-        const uint32_t dst = smem_addr(v_smem + s * KV_BYTES);
-        mbar_expect_tx(v_full0 + 8 * s, KV_BYTES);
+        if (i >= V_STAGES && !stage_free(v_empty0 + 8 * s, ((i / V_STAGES) - 1) & 1)) return false;
+        if (POOLED && i < n_pp) {
+          gather(v_smem + s * KV_BYTES, i, 1, v_full0 + 8 * s);
+        } else if (lane == 0) {
+          const int row = ((pt[i - n_pp] * planes + (planes - 1)) * nkv + kvh) * PAGE;      // one panel: it is keys and values
+          const uint32_t dst = smem_addr(v_smem + s * KV_BYTES);
+          mbar_expect_tx(v_full0 + 8 * s, KV_BYTES);
 #pragma unroll
-        for (int sub = 0; sub < SUBS; ++sub)
-          tma_load_2d(dst + sub * KV_SUB_BYTES, &map_kv, 64 * sub, row, v_full0 + 8 * s);
+          for (int sub = 0; sub < SUBS; ++sub)
+            tma_load_2d(dst + sub * KV_SUB_BYTES, &map_kv, 64 * sub, row, v_full0 + 8 * s);
+        }
+        if (POOLED) __syncwarp();
         return true;
       };
       // in the order of use: K0, K1, V0, K2, V1, K3, ...
@@ -217,7 +276,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         if (i + 1 < n_pages) ok = load_k(i + 1);
         if (ok) ok = load_v(i);
       }
-      if (!ok) atomicExch(status, ST_PRODUCER);
+      if (!ok && lane == 0) atomicExch(status, ST_PRODUCER);
     }
   } else if (warp == SOFTMAX_WARPS + 1) {
     if (lane == 0) {
@@ -290,6 +349,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     const int pos_a = pos0 + rA, pos_b = pos0 + rB;
     const int lo_a = first_visible_key(pos_a, window);
     const int lo_b = first_visible_key(pos_b, window);
+    // blocks that the two rows see (pooled panels only)
+    const int nb_a = POOLED ? max(0, pos_a - window + 1) / pool : 0;
+    const int nb_b = POOLED ? max(0, pos_b - window + 1) / pool : 0;
     const uint32_t lane_base = tmem + ((uint32_t)row0 << 16);
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;      // l: this thread's keys only
     bool ok = true;
@@ -311,21 +373,26 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       tmem_ld_16x256b_x8(sbuf, sr);
       tmem_ld_wait();
       TOCK(6, t_ld);
-      const int key0 = (first_page + i) * PAGE;
+      // a pooled panel counts in blocks: block j is seen by a row while j < the row's block count
+      const bool in_pool = POOLED && i < n_pp;
+      const int key0 = in_pool ? i * PAGE : (first_page + i - n_pp) * PAGE;
+      const int hi_a = in_pool ? nb_a - 1 : pos_a, hi_b = in_pool ? nb_b - 1 : pos_b;
+      const int lw_a = in_pool ? 0 : lo_a, lw_b = in_pool ? 0 : lo_b;
       TICK(t_mx);
       // raw scores stay in sr; the scale (> 0) is applied to the maximum and inside the exponent.
       // Only pages that cross the limits of the warp's rows are masked (warp-uniform test).
       const int warp_pos_min = pos0 + row0, warp_pos_max = warp_pos_min + 15;
-      const bool partial = key0 + PAGE - 1 > warp_pos_min ||
-                           (window != 0 && key0 < first_visible_key(warp_pos_max, window));
+      const bool partial = in_pool ? key0 + PAGE > max(0, warp_pos_min - window + 1) / pool
+                                   : key0 + PAGE - 1 > warp_pos_min ||
+                                         (window != 0 && key0 < first_visible_key(warp_pos_max, window));
       if (partial) {
 #pragma unroll
         for (int j = 0; j < 8; ++j)
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int key = key0 + 8 * j + 2 * c + e;
-            if (key > pos_a || key < lo_a) sr[4 * j + e] = 0xff800000u;           // -inf
-            if (key > pos_b || key < lo_b) sr[4 * j + 2 + e] = 0xff800000u;
+            if (key > hi_a || key < lw_a) sr[4 * j + e] = 0xff800000u;           // -inf
+            if (key > hi_b || key < lw_b) sr[4 * j + 2 + e] = 0xff800000u;
           }
       }
       float mxa[2] = {-INFINITY, -INFINITY}, mxb[2] = {-INFINITY, -INFINITY};       // short chains
@@ -455,11 +522,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 
 // q, out [T, nh*HD] bfloat16; cache [n_pages][2][nkv][64][HD] bfloat16 of one layer;
 // tiles [n_tiles][4] int32 = {sequence, first token, rows (<= 128), position of row 0}.
-extern "C" int g2b_attn_prefill_tc(const void *q, void *out, const void *cache, long long n_cache_pages,
-                                   const int *tiles, int n_tiles, const int *page_table, int P,
-                                   int T, int nh, int nkv, int hd, int page_size, int window,
-                                   float scale, const float *sink, int planes, int q_stride,
-                                   const void *gate, int gate_stride, int *status, cudaStream_t stream) {
+// `pooled` (or null) [n_pages][2][nkv][pool_rows][HD]: the means of whole blocks of `pool` positions.
+static int launch_prefill_tc(const void *q, void *out, const void *cache, long long n_cache_pages,
+                             const int *tiles, int n_tiles, const int *page_table, int P,
+                             int T, int nh, int nkv, int hd, int page_size, int window,
+                             float scale, const float *sink, int planes, int q_stride,
+                             const void *gate, int gate_stride, const void *pooled, int pool, int pool_rows,
+                             int *status, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (hd != HD) G2B_REFUSE("attn_prefill_tc: built for head_dim %d, got %d", HD, hd);
   if (page_size != PAGE) G2B_REFUSE("attn_prefill_tc: page size must be %d, got %d", PAGE, page_size);
@@ -472,6 +541,10 @@ extern "C" int g2b_attn_prefill_tc(const void *q, void *out, const void *cache, 
     G2B_REFUSE("attn_prefill_tc: q, out and the cache must be 16-byte aligned");
   if (n_cache_pages * planes * nkv * PAGE > 0x7fffffffLL)
     G2B_REFUSE("attn_prefill_tc: the cache layer has too many rows for 32-bit copy coordinates");
+  if (pooled && (pool <= 0 || window <= 0 || planes != 2 || sink || gate || pool_rows < (PAGE + pool - 1) / pool ||
+                 ((uintptr_t)pooled & 15)))
+    G2B_REFUSE("attn_prefill_tc: pooled blocks of %d need a window, %d rows a page, a 16-byte aligned store, and go "
+               "with neither a sink nor a gate", pool, pool > 0 ? (PAGE + pool - 1) / pool : 0);
   CUtensorMap mq, mkv;
   int rc = get_map(&mq, q, T, nh * HD, q_stride, BM);
   if (rc) G2B_REFUSE("attn_prefill_tc: tensor map of q failed (%d)", rc);
@@ -484,15 +557,44 @@ extern "C" int g2b_attn_prefill_tc(const void *q, void *out, const void *cache, 
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel,
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
     if (e != cudaSuccess) G2B_REFUSE("attn_prefill_tc: shared memory: %s", cudaGetErrorString(e));
-    cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    cudaFuncSetAttribute(attn_prefill_tc_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    cudaFuncSetAttribute(attn_prefill_tc_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     if (cfg_dev >= 0) configured.value[cfg_dev] = n_sms;
   }
-  g2b_launch(attn_prefill_tc_kernel, dim3((unsigned)n_tiles * nh), dim3(THREADS), SMEM_TOTAL, stream, mq, mkv,
-             (bf16 *)out, (const int4 *)tiles, page_table, P, nh, nkv, window, scale * LOG2E, n_sms, status, sink, planes, (const bf16 *)gate, gate_stride);
+  if (pooled)
+    g2b_launch(attn_prefill_tc_kernel<true>, dim3((unsigned)n_tiles * nh), dim3(THREADS), SMEM_TOTAL, stream, mq, mkv,
+               (bf16 *)out, (const int4 *)tiles, page_table, P, nh, nkv, window, scale * LOG2E, n_sms, status, sink,
+               planes, (const bf16 *)gate, gate_stride, (const bf16 *)pooled, pool, pool_rows);
+  else
+    g2b_launch(attn_prefill_tc_kernel<false>, dim3((unsigned)n_tiles * nh), dim3(THREADS), SMEM_TOTAL, stream, mq, mkv,
+               (bf16 *)out, (const int4 *)tiles, page_table, P, nh, nkv, window, scale * LOG2E, n_sms, status, sink,
+               planes, (const bf16 *)gate, gate_stride, (const bf16 *)nullptr, 0, 0);
   return g2b_check_launch("attn_prefill_tc");
+}
+
+extern "C" int g2b_attn_prefill_tc(const void *q, void *out, const void *cache, long long n_cache_pages,
+                                   const int *tiles, int n_tiles, const int *page_table, int P,
+                                   int T, int nh, int nkv, int hd, int page_size, int window,
+                                   float scale, const float *sink, int planes, int q_stride,
+                                   const void *gate, int gate_stride, int *status, cudaStream_t stream) {
+  return launch_prefill_tc(q, out, cache, n_cache_pages, tiles, n_tiles, page_table, P, T, nh, nkv, hd, page_size,
+                           window, scale, sink, planes, q_stride, gate, gate_stride, nullptr, 0, 0, status, stream);
+}
+
+// The same over a window of tokens and, in front of it, the pooled blocks of `pool` positions.
+extern "C" int g2b_attn_prefill_tc_pooled(const void *q, void *out, const void *cache, long long n_cache_pages,
+                                          const int *tiles, int n_tiles, const int *page_table, int P,
+                                          int T, int nh, int nkv, int hd, int page_size, int window,
+                                          float scale, int q_stride, const void *pooled, int pool, int pool_rows,
+                                          int *status, cudaStream_t stream) {
+  if (!pooled || pool <= 0) G2B_REFUSE("attn_prefill_tc_pooled: no store of pooled blocks (pool %d)", pool);
+  return launch_prefill_tc(q, out, cache, n_cache_pages, tiles, n_tiles, page_table, P, T, nh, nkv, hd, page_size,
+                           window, scale, nullptr, 2, q_stride, nullptr, 0, pooled, pool, pool_rows, status, stream);
 }
 
 extern "C" int g2b_attn_prefill_tc_tile_rows() { return BM; }

@@ -339,8 +339,26 @@ def attention_bf16(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page
 def attention_pooled_bf16(q, out, cache_pages, pooled, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
                           pool, scale) -> bool:
     """Attention over a window of tokens and the pooled blocks in front of it on the tensor cores;
-    False: the case is left to the 32-bit kernel."""
-    return False
+    False: the case is left to the kernel of CUDA cores.  Prompt tiles run the tcgen05 kernel, whose
+    producer warp gathers the pooled blocks into panels in front of the window's pages; single tokens
+    (a window's keys and a few blocks each) stay with the other kernel."""
+    if head_dim not in FAST_HEAD_SIZES or page_size != 64 or cache_pages.dtype != torch.bfloat16:
+        return False
+    if q.stride(1) != 1 or q.stride(0) % 8 or q.data_ptr() % 16 or not out.is_contiguous():
+        return False
+    if not scale > 0.0 or window <= 0 or pool <= 0 or not USE_TC_ATTENTION or ctx.all_single:
+        return False
+    if getattr(ctx, "attn_tiles_wide", None) is None or ctx.n_attn_tiles_wide <= 0:
+        return False
+    f = _fn("attn_prefill_tc.cu", "g2b_attn_prefill_tc_pooled",
+            [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+             c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p],
+            defines=(f"HD={head_dim}",))
+    _call(f, _ptr(q), _ptr(out), _ptr(cache_pages), cache_pages.shape[0], _ptr(ctx.attn_tiles_wide),
+          ctx.n_attn_tiles_wide, _ptr(ctx.page_table), ctx.page_table.shape[1], q.shape[0], n_heads,
+          n_kv_heads, head_dim, page_size, window, scale, q.stride(0), _ptr(pooled), int(pool),
+          pooled.shape[3], _ptr(_status_word(q.device)), _stream())
+    return True
 
 
 USE_TC_ATTENTION = True      # prompt attention on tcgen05 (else the mma.sync kernel)

@@ -39,7 +39,14 @@ def step_ctx(q_lens, pasts, slots, dtype, pages=None, single=False):
     meta = np.array([[s, n, p, sl] for s, n, p, sl in zip(starts, q_lens, pasts, slots)])
     T = int(sum(q_lens))
     table = i32(pages if pages is not None else [[0]] * len(q_lens))
-    return StepContext(n_tokens=T, n_seqs=len(q_lens), tok_ids=i32(np.zeros(T)), tok_pos=i32(pos), tok_seq=i32(seq),
+    tiles = {}
+    if not single:                                    # the prompt kernels' work lists: tiles of 64 and of 128 rows
+        for key, rows in (("attn_tiles", 64), ("attn_tiles_wide", 128)):
+            t = [(b, int(s) + r, min(rows, n - r), p + r) for b, (s, n, p) in enumerate(zip(starts, q_lens, pasts))
+                 for r in range(0, n, rows)]
+            t.sort(key=lambda x: -(x[3] + x[2]))
+            tiles[key], tiles["n_" + key] = i32(t), len(t)
+    return StepContext(**tiles, n_tokens=T, n_seqs=len(q_lens), tok_ids=i32(np.zeros(T)), tok_pos=i32(pos), tok_seq=i32(seq),
                        page_table=table, page_size=64, workspace=Workspace(DEV), dtype=DTYPES[dtype],
                        q_lens=list(q_lens), past_lens=list(pasts), slots=list(slots),
                        max_kv_len=int(max(p + n for p, n in zip(pasts, q_lens))),

@@ -157,6 +157,27 @@ def test_a_block_far_back_among_hundreds(decode):
     assert np.abs(got[-30:] - ref[-30:]).max() < 1e-3 * share
 
 
+@pytest.mark.parametrize("D,window,pool", [(64, 10, 2), (128, 40, 3), (64, 130, 1)])
+def test_hundreds_of_blocks_in_front_of_a_prompt_tile(D, window, pool):
+    """16-bit prompts on the tensor cores: 900 tokens give several panels of 64 blocks in front of the
+    window's pages, a last panel that is partly filled, and tiles whose rows see different numbers of
+    blocks.  Two early tokens are flagged so that their blocks carry weight in every late row; the cuts
+    put a tile's first row before, on and behind a block's and a page's edge."""
+    m, W, width = flagged_attention(window, pool, D=D, rot=D // 2, bump=6.0 * pool)
+    part = attention_part(m, W, width, "bfloat16")
+    rng = np.random.default_rng(D + pool)
+    hs = [flagged_rows(rng, 900, width, [5, 401]), flagged_rows(rng, 333, width, [64])]
+    ref = [SP.attention_mixer(h, W, "", m, EPS, round_cache=bf) for h in hs]
+    plain = hs[0].copy()
+    plain[[5, 401], 0] = 0.0
+    share = np.abs(ref[0][-50:] - SP.attention_mixer(plain, W, "", m, EPS, round_cache=bf)[-50:]).max()
+    assert share > 0.1 * np.abs(ref[0][-50:]).max()
+    for cuts in (([], []), ([129, 500], [200]), ([window + pool, 64, 2, 381], [65, 3]), ([700] + [1] * 200, [300] + [1] * 33)):
+        got = run_part(part, part.cache_need(), hs, cuts, "bfloat16", pages_per_seq=15)
+        for b in range(2):
+            close(got[b], ref[b], "bfloat16", f"blocks in front of a tile {cuts[0][:3]} sequence {b}")
+
+
 def test_first_tokens_of_a_sequence():
     """The first query sees itself alone (its output is its own normed value through the output
     product); the first ``window`` queries see everything so far and no block."""
