@@ -1021,7 +1021,21 @@ scan_gates_max_kernel(const T *__restrict__ xi, const T *__restrict__ xf, int x_
         const int hh = threadIdx.x + 256 * e;
         if (hh < Hn) {
           float mm = e == 0 ? m : m_hi[e];
-          for (int tt = 0; tt < nt; ++tt) {
+          // eight tokens' gates are fetched before their maxima are chained, so that a link of the
+          // chain is an addition and a maximum, not a wait on shared memory
+          int tt = 0;
+          for (; tt + 8 <= nt; tt += 8) {
+            float f8[8], i8[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) f8[u] = sf[(tt + u) * Hn + hh], i8[u] = si[(tt + u) * Hn + hh];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              sm_old[(tt + u) * Hn + hh] = mm;
+              mm = fmaxf(f8[u] + mm, i8[u]);
+              sm_new[(tt + u) * Hn + hh] = mm;
+            }
+          }
+          for (; tt < nt; ++tt) {
             const int idx = tt * Hn + hh;
             sm_old[idx] = mm;
             mm = fmaxf(sf[idx] + mm, si[idx]);

@@ -17,7 +17,7 @@ units.SPECIALISED_SOURCES[:] = [("attn_decode.cu", ()), ("attn_decode.cu", ("ATT
                                 ("attn_decode.cu", ("ATTN_DECODE_PAGES=6",)), ("attn_decode.cu", ("ATTN_DECODE_PAGES=8",)),
                                 ("attn_decode_noalloc.cu", ()),
                                 ("attn_prefill.cu", ()), ("attn_prefill_tc.cu", ()),
-                                ("attn_prefill_tc_split.cu", ())]
+                                ("attn_prefill_tc_split.cu", ()), ("attn_pool_decode.cu", ())]
 units.BF16_UNITS[:] = [("gemm_small.cu", ()), ("gemm_tc.cu", ())]
 
 
@@ -340,13 +340,23 @@ def attention_pooled_bf16(q, out, cache_pages, pooled, ctx, n_heads, n_kv_heads,
                           pool, scale) -> bool:
     """Attention over a window of tokens and the pooled blocks in front of it on the tensor cores;
     False: the case is left to the kernel of CUDA cores.  Prompt tiles run the tcgen05 kernel, whose
-    producer warp gathers the pooled blocks into panels in front of the window's pages; single tokens
-    (a window's keys and a few blocks each) stay with the other kernel."""
+    producer warp gathers the pooled blocks into panels in front of the window's pages; steps of single
+    tokens (a window's keys and a few blocks each) run a kernel of their own, laid out for latency."""
     if head_dim not in FAST_HEAD_SIZES or page_size != 64 or cache_pages.dtype != torch.bfloat16:
         return False
     if q.stride(1) != 1 or q.stride(0) % 8 or q.data_ptr() % 16 or not out.is_contiguous():
         return False
-    if not scale > 0.0 or window <= 0 or pool <= 0 or not USE_TC_ATTENTION or ctx.all_single:
+    if window <= 0 or pool <= 0:
+        return False
+    if ctx.all_single:
+        f = _fn("attn_pool_decode.cu", "g2b_attn_pool_decode",
+                [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                 c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p], defines=(f"HD={head_dim}",))
+        _call(f, _ptr(q), _ptr(out), _ptr(cache_pages), _ptr(pooled), _ptr(ctx.tok_pos), _ptr(ctx.tok_seq),
+              _ptr(ctx.page_table), ctx.page_table.shape[1], q.shape[0], n_heads, n_kv_heads, head_dim, page_size,
+              window, scale, q.stride(0), int(pool), pooled.shape[3], _stream())
+        return True
+    if not scale > 0.0 or not USE_TC_ATTENTION:
         return False
     if getattr(ctx, "attn_tiles_wide", None) is None or ctx.n_attn_tiles_wide <= 0:
         return False

@@ -61,6 +61,7 @@ def attention_config(H, G, D, V, window, pool, rot, scaling=None, scale=None):
     (2, 2, 40, 24, 3, 10, 0, None),                      # tokens that no query sees for a while; no rotation
     (3, 1, 16, 16, 50, 0, 16, (4.0, 32, 4.0, 1.0)),      # a window without blocks
     (2, 2, 32, 16, 0, 0, 16, None),                      # everything seen
+    (5, 1, 64, 64, 20, 4, 32, None),                     # more query heads on a kv head than one block of threads takes
 ])
 def test_attention_part(H, G, D, V, window, pool, rot, scaling, dtype):
     """Value norm, stretched rotation of part of a head, the score scale, the window and the blocks in
