@@ -673,11 +673,55 @@ __global__ void swiglu_kernel(const T *__restrict__ gu, T *__restrict__ out, lon
   out[idx] = from_f32<T>((g / (1.f + expf(-g))) * u);
 }
 
+// The same in bfloat16 for blocks of a multiple of eight: a thread takes eight neighbouring outputs,
+// their gates and their ups as one 16-byte load each.
+__global__ void __launch_bounds__(256)
+swiglu8_kernel(const bf16 *__restrict__ gu, bf16 *__restrict__ out, long long total8, int I, int blk, float limit,
+               float alpha) {
+  pdl_launch();
+  pdl_wait();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total8) return;
+  const int per_row = I / 8;
+  const long long t = idx / per_row;
+  const int i = (int)(idx % per_row) * 8;
+  const int b = i / blk, r = i % blk;
+  const bf16 *src = gu + (size_t)t * 2 * I + (size_t)2 * blk * b + r;
+  const uint4 gv = __ldg(reinterpret_cast<const uint4 *>(src));
+  const uint4 uv = __ldg(reinterpret_cast<const uint4 *>(src + blk));
+  const unsigned int gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+  unsigned int ow[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&gw[e]));
+    float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&uw[e]));
+    float2 o;
+    if (limit > 0.f) {
+      g.x = fminf(g.x, limit), g.y = fminf(g.y, limit);
+      u.x = fminf(fmaxf(u.x, -limit), limit), u.y = fminf(fmaxf(u.y, -limit), limit);
+      o.x = (g.x / (1.f + expf(-alpha * g.x))) * (u.x + 1.f);
+      o.y = (g.y / (1.f + expf(-alpha * g.y))) * (u.y + 1.f);
+    } else {
+      o.x = (g.x / (1.f + expf(-g.x))) * u.x;
+      o.y = (g.y / (1.f + expf(-g.y))) * u.y;
+    }
+    const __nv_bfloat162 ob = __floats2bfloat162_rn(o.x, o.y);
+    ow[e] = *reinterpret_cast<const unsigned int *>(&ob);
+  }
+  *reinterpret_cast<uint4 *>(out + (size_t)t * I + i) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+}
+
 extern "C" int g2b_swiglu(const void *gu, int dtype, int T_tokens, int I, int blk, void *out,
                           float limit, float alpha, cudaStream_t stream) {
   if (T_tokens <= 0) return 0;
   if (I <= 0 || blk <= 0 || I % blk) G2B_REFUSE("swiglu: block %d does not divide width %d", blk, I);
   const long long total = (long long)T_tokens * I;
+  if (dtype == G2B_BF16 && blk % 8 == 0 && !(((uintptr_t)gu | (uintptr_t)out) & 15)) {
+    const long long total8 = total / 8;
+    g2b_launch(swiglu8_kernel, dim3((unsigned)((total8 + 255) / 256)), dim3(256), 0, stream, (const bf16 *)gu, (bf16 *)out,
+               total8, I, blk, limit, alpha);
+    return g2b_check_launch("swiglu");
+  }
   const unsigned blocks = (unsigned)((total + 255) / 256);
   if (dtype == G2B_F32)
     g2b_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float *)gu, (float *)out, total, I, blk, limit, alpha);

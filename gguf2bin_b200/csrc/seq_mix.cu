@@ -226,6 +226,59 @@ short_conv_kernel(const T *__restrict__ x, int x_stride, const float *__restrict
   out[(size_t)t * out_stride + c] = from_f32<T>(act ? silu_f(acc) : acc);
 }
 
+// The same in bfloat16 for channel counts and row strides that are multiples of eight: a thread takes
+// eight neighbouring channels of a token, 16 bytes of every tap's row at a time.
+__global__ void __launch_bounds__(128)
+short_conv8_kernel(const bf16 *__restrict__ x, int x_stride, const float *__restrict__ w, bf16 *__restrict__ ring,
+                   int taps, int C, const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
+                   const int *__restrict__ seq_slots, const int *__restrict__ seq_meta, int act,
+                   bf16 *__restrict__ out, int out_stride, const float *__restrict__ bias) {
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (c >= C) return;
+  const int b = tok_seq[t], pos = tok_pos[t];
+  const int first_row = seq_meta ? seq_meta[4 * b + 0] : t;
+  const int past = seq_meta ? seq_meta[4 * b + 2] : pos;
+  bf16 *my_ring = ring + (size_t)seq_slots[b] * taps * C;
+  float acc[8];
+  if (bias) {
+    const float4 b0 = *reinterpret_cast<const float4 *>(bias + c), b1 = *reinterpret_cast<const float4 *>(bias + c + 4);
+    acc[0] = b0.x, acc[1] = b0.y, acc[2] = b0.z, acc[3] = b0.w, acc[4] = b1.x, acc[5] = b1.y, acc[6] = b1.z, acc[7] = b1.w;
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  }
+  for (int j = 0; j < taps; ++j) {
+    const int p = pos - (taps - 1) + j;
+    if (p < 0) continue;                               // zeros in front of the sequence
+    const bf16 *src = p >= past ? x + (size_t)(first_row + (p - past)) * x_stride + c : my_ring + (size_t)(p % taps) * C + c;
+    const uint4 xv = *reinterpret_cast<const uint4 *>(src);
+    const float4 w0 = __ldg(reinterpret_cast<const float4 *>(w + (size_t)j * C + c));
+    const float4 w1 = __ldg(reinterpret_cast<const float4 *>(w + (size_t)j * C + c + 4));
+    const float2 x0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&xv.x));
+    const float2 x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&xv.y));
+    const float2 x2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&xv.z));
+    const float2 x3 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&xv.w));
+    acc[0] = fmaf(w0.x, x0.x, acc[0]), acc[1] = fmaf(w0.y, x0.y, acc[1]);
+    acc[2] = fmaf(w0.z, x1.x, acc[2]), acc[3] = fmaf(w0.w, x1.y, acc[3]);
+    acc[4] = fmaf(w1.x, x2.x, acc[4]), acc[5] = fmaf(w1.y, x2.y, acc[5]);
+    acc[6] = fmaf(w1.z, x3.x, acc[6]), acc[7] = fmaf(w1.w, x3.y, acc[7]);
+  }
+  if (!seq_meta && taps > 1)      // one token per sequence: place pos % taps of the slot's ring is not read above
+    *reinterpret_cast<uint4 *>(my_ring + (size_t)(pos % taps) * C + c) =
+        *reinterpret_cast<const uint4 *>(x + (size_t)t * x_stride + c);
+  unsigned int ow[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float a = act ? silu_f(acc[2 * e]) : acc[2 * e], d = act ? silu_f(acc[2 * e + 1]) : acc[2 * e + 1];
+    const __nv_bfloat162 ob = __floats2bfloat162_rn(a, d);
+    ow[e] = *reinterpret_cast<const unsigned int *>(&ob);
+  }
+  *reinterpret_cast<uint4 *>(out + (size_t)t * out_stride + c) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 conv_keep_kernel(const T *__restrict__ x, int x_stride, T *__restrict__ ring, int taps, int C, int n_seqs,
@@ -257,8 +310,14 @@ extern "C" int g2b_short_conv(const void *x, int dtype, int x_stride, const floa
       g2b_launch(conv_keep_kernel<float>, keep_grid, dim3(256), 0, stream, (const float *)x, x_stride, (float *)ring, taps, C,
                  n_seqs, seq_meta);
   } else if (dtype == G2B_BF16) {
-    g2b_launch(short_conv_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16 *)x, x_stride, w, (bf16 *)ring, taps, C,
-               T_tokens, tok_pos, tok_seq, seq_slots, seq_meta, act, (bf16 *)out, out_stride, bias);
+    const bool wide = C % 8 == 0 && x_stride % 8 == 0 && out_stride % 8 == 0 && (C + 1023) / 1024 <= 65535 &&
+                      !(((uintptr_t)x | (uintptr_t)out | (uintptr_t)ring | (uintptr_t)w | (uintptr_t)bias) & 15);
+    if (wide)
+      g2b_launch(short_conv8_kernel, dim3(T_tokens, (C / 8 + 127) / 128), dim3(128), 0, stream, (const bf16 *)x, x_stride, w,
+                 (bf16 *)ring, taps, C, tok_pos, tok_seq, seq_slots, seq_meta, act, (bf16 *)out, out_stride, bias);
+    else
+      g2b_launch(short_conv_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16 *)x, x_stride, w, (bf16 *)ring, taps, C,
+                 T_tokens, tok_pos, tok_seq, seq_slots, seq_meta, act, (bf16 *)out, out_stride, bias);
     if (seq_meta && taps > 1)
       g2b_launch(conv_keep_kernel<bf16>, keep_grid, dim3(256), 0, stream, (const bf16 *)x, x_stride, (bf16 *)ring, taps, C,
                  n_seqs, seq_meta);
