@@ -6,10 +6,11 @@
 // A step of single tokens has little work per token (a window and context / pool blocks), so the
 // kernel is laid out for latency: a CTA takes one token and up to GH query heads that share a kv
 // head, and walks the token's list (blocks first, then the window's keys) in passes of PASS entries.
-//   scores:   a warp takes every 8th entry; its lanes split the row (one 4- or 8-byte load each),
-//             one warp sum per query head; the V row's address is kept for the third phase;
+//   scores:   a thread takes one entry and reads its whole key row with 16-byte loads that are all in
+//             flight at once (the queries come from shared memory, every thread the same address); the
+//             V row's address is kept for the third phase;
 //   softmax:  warp g owns head g: the pass's maximum, the running maximum and sum, the weights;
-//   values:   a thread owns two neighbouring value dimensions of every NS-th entry of the pass.
+//   values:   HD / 8 threads cover a value row, 16 bytes each; a slice of them takes every NS-th entry.
 // The partial sums of the NS slices meet once, at the end.  The order of every sum depends on the
 // token's position only: not on the batch, nor on how the sequence reached that position.
 //
@@ -28,21 +29,19 @@ namespace {
 constexpr int PAGE = 64;
 constexpr int THREADS = 256, WARPS = THREADS / 32;
 constexpr int GH = 4;                       // query heads of one kv head that a CTA takes
-constexpr int PASS = 256;                   // entries (blocks or keys) per pass
-constexpr int EPL = HD / 32;                // elements of a row per lane
-constexpr int NS = THREADS / (HD / 2);      // slices of a pass in the value phase
+constexpr int PASS = THREADS;               // entries (blocks or keys) per pass: one per thread
+constexpr int TPR = HD / 8;                 // threads that cover a value row, 16 bytes each
+constexpr int NS = THREADS / TPR;           // slices of a pass in the value phase
 static_assert(GH <= WARPS, "a warp per head in the softmax phase");
 
-// N (2 or 4) neighbouring bfloat16 as floats, fetched with one load
-template <int N> __device__ __forceinline__ void load_part(const bf16 *p, float *f) {
-  if constexpr (N == 2) {
-    const float2 a = __bfloat1622float2(__ldg(reinterpret_cast<const __nv_bfloat162 *>(p)));
-    f[0] = a.x, f[1] = a.y;
-  } else {
-    const uint2 v = __ldg(reinterpret_cast<const uint2 *>(p));
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&v.x));
-    const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&v.y));
-    f[0] = a.x, f[1] = a.y, f[2] = c.x, f[3] = c.y;
+// eight neighbouring bfloat16 as floats, fetched with one 16-byte load
+__device__ __forceinline__ void load8(const bf16 *p, float *f) {
+  const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p));
+  const unsigned int w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w[e]));
+    f[2 * e] = a.x, f[2 * e + 1] = a.y;
   }
 }
 }  // namespace
@@ -54,10 +53,11 @@ attn_pool_decode_kernel(const bf16 *__restrict__ q, bf16 *__restrict__ out, cons
                         int nkv, int window, float scale, int q_stride, int pool, int pool_rows) {
   pdl_launch();
   pdl_wait();
+  __shared__ __align__(16) float qs[GH][HD];           // the queries
   __shared__ float sc[GH][PASS];                       // scores, then weights, of the pass
   __shared__ const bf16 *vrow[PASS];                   // where each entry's value row starts
   __shared__ float s_m[GH], s_l[GH], s_corr[GH];
-  __shared__ float red[NS][GH][HD];
+  __shared__ float red[WARPS][GH][HD];
 
   const int t = blockIdx.x;
   const int group = nh / nkv, head_tiles = (group + GH - 1) / GH;
@@ -71,30 +71,25 @@ attn_pool_decode_kernel(const bf16 *__restrict__ q, bf16 *__restrict__ out, cons
   const int *pt = page_table + (size_t)b * P;
   const size_t panel = (size_t)PAGE * HD, ppanel = (size_t)pool_rows * HD;
 
-  float qr[GH][EPL];                                   // this lane's part of each head's query
-#pragma unroll
-  for (int g = 0; g < GH; ++g) {
-    if (g < n_heads) {
-      load_part<EPL>(q + (size_t)t * q_stride + (size_t)(h0 + g) * HD + lane * EPL, qr[g]);
-    } else {
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) qr[g][e] = 0.f;
-    }
+  for (int idx = threadIdx.x; idx < GH * HD; idx += THREADS) {
+    const int g = idx / HD, d = idx % HD;
+    qs[g][d] = g < n_heads ? __bfloat162float(q[(size_t)t * q_stride + (size_t)(h0 + g) * HD + d]) : 0.f;
   }
   if (threadIdx.x < GH) s_m[threadIdx.x] = -INFINITY, s_l[threadIdx.x] = 0.f;
 
-  const int dp = threadIdx.x % (HD / 2), slice = threadIdx.x / (HD / 2);
-  float acc[GH][2];
+  const int d8 = (threadIdx.x % TPR) * 8, slice = threadIdx.x / TPR;
+  float acc[GH][8];
 #pragma unroll
-  for (int g = 0; g < GH; ++g) acc[g][0] = acc[g][1] = 0.f;
+  for (int g = 0; g < GH; ++g)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
 
   for (int i0 = 0; i0 < n_entries; i0 += PASS) {
     const int n_here = min(PASS, n_entries - i0);
-    __syncthreads();                                   // the last pass's weights are used up; s_m, s_l are set
-    // ---- scores ----
-#pragma unroll 2
-    for (int r = warp; r < n_here; r += WARPS) {
-      const int i = i0 + r;
+    __syncthreads();                                   // the last pass's weights are used up; qs, s_m, s_l are set
+    // ---- scores: a thread takes one entry and reads its whole key row, all loads in flight at once ----
+    if (threadIdx.x < n_here) {
+      const int i = i0 + threadIdx.x;
       const bf16 *krow, *vr;
       if (i < n_blocks) {
         const int home = (i * pool) / PAGE;
@@ -106,22 +101,26 @@ attn_pool_decode_kernel(const bf16 *__restrict__ q, bf16 *__restrict__ out, cons
         krow = cache + (((size_t)pt[key / PAGE] * 2) * nkv + kvh) * panel + (size_t)(key % PAGE) * HD;
         vr = krow + (size_t)nkv * panel;
       }
-      float kf[EPL];
-      load_part<EPL>(krow + lane * EPL, kf);
+      vrow[threadIdx.x] = vr;
       float dot[GH];
 #pragma unroll
-      for (int g = 0; g < GH; ++g) {
-        dot[g] = 0.f;
+      for (int g = 0; g < GH; ++g) dot[g] = 0.f;
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) dot[g] = fmaf(qr[g][e], kf[e], dot[g]);
+      for (int c = 0; c < HD / 8; ++c) {
+        float kf[8];
+        load8(krow + 8 * c, kf);
+#pragma unroll
+        for (int g = 0; g < GH; ++g) {
+          const float4 q0 = *reinterpret_cast<const float4 *>(&qs[g][8 * c]);      // every thread the same address
+          const float4 q1 = *reinterpret_cast<const float4 *>(&qs[g][8 * c + 4]);
+          dot[g] = fmaf(q0.x, kf[0], dot[g]), dot[g] = fmaf(q0.y, kf[1], dot[g]);
+          dot[g] = fmaf(q0.z, kf[2], dot[g]), dot[g] = fmaf(q0.w, kf[3], dot[g]);
+          dot[g] = fmaf(q1.x, kf[4], dot[g]), dot[g] = fmaf(q1.y, kf[5], dot[g]);
+          dot[g] = fmaf(q1.z, kf[6], dot[g]), dot[g] = fmaf(q1.w, kf[7], dot[g]);
+        }
       }
 #pragma unroll
-      for (int g = 0; g < GH; ++g) dot[g] = warp_sum(dot[g]);
-      if (lane == 0) {
-        vrow[r] = vr;
-#pragma unroll
-        for (int g = 0; g < GH; ++g) sc[g][r] = dot[g] * scale;
-      }
+      for (int g = 0; g < GH; ++g) sc[g][threadIdx.x] = dot[g] * scale;
     }
     __syncthreads();
     // ---- softmax: warp g owns head g ----
@@ -145,31 +144,44 @@ attn_pool_decode_kernel(const bf16 *__restrict__ q, bf16 *__restrict__ out, cons
       }
     }
     __syncthreads();
-    // ---- values ----
+    // ---- values: TPR threads cover a row, slice s takes the entries s, s + NS, ... ----
 #pragma unroll
     for (int g = 0; g < GH; ++g) {
       const float corr = g < n_heads ? s_corr[g] : 0.f;
-      acc[g][0] *= corr, acc[g][1] *= corr;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[g][e] *= corr;
     }
 #pragma unroll 4
     for (int r = slice; r < n_here; r += NS) {
-      const float2 v = __bfloat1622float2(__ldg(reinterpret_cast<const __nv_bfloat162 *>(vrow[r]) + dp));
+      float vf[8];
+      load8(vrow[r] + d8, vf);
 #pragma unroll
       for (int g = 0; g < GH; ++g) {
-        const float p = sc[g][r];                      // rows of heads that are not there hold old numbers: not written out
-        acc[g][0] = fmaf(p, v.x, acc[g][0]);
-        acc[g][1] = fmaf(p, v.y, acc[g][1]);
+        const float p = sc[g][r];                      // rows of heads that are not there hold zeros' scores: not written out
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(p, vf[e], acc[g][e]);
       }
     }
   }
+  // the slices of one warp meet in its first TPR lanes, the warps in shared memory
 #pragma unroll
-  for (int g = 0; g < GH; ++g) red[slice][g][2 * dp] = acc[g][0], red[slice][g][2 * dp + 1] = acc[g][1];
+  for (int off = TPR; off < 32; off <<= 1)
+#pragma unroll
+    for (int g = 0; g < GH; ++g)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[g][e] += __shfl_xor_sync(0xffffffffu, acc[g][e], off);
+  if (lane < TPR) {
+#pragma unroll
+    for (int g = 0; g < GH; ++g)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) red[warp][g][d8 + e] = acc[g][e];
+  }
   __syncthreads();
   for (int idx = threadIdx.x; idx < n_heads * HD; idx += THREADS) {
     const int g = idx / HD, d = idx % HD;
     float sum = 0.f;
 #pragma unroll
-    for (int s = 0; s < NS; ++s) sum += red[s][g][d];
+    for (int w = 0; w < WARPS; ++w) sum += red[w][g][d];
     out[(size_t)t * nh * HD + (size_t)(h0 + g) * HD + d] = __float2bfloat16(sum / s_l[g]);
   }
 }
@@ -186,8 +198,8 @@ extern "C" int g2b_attn_pool_decode(const void *q, void *out, const void *cache,
   if (pool <= 0 || window <= 0 || !pooled || pool_rows < (PAGE + pool - 1) / pool)
     G2B_REFUSE("attn_pool_decode: pooled blocks of %d need a window, their store and %d rows a page", pool,
                pool > 0 ? (PAGE + pool - 1) / pool : 0);
-  if (q_stride < nh * HD || q_stride % 4 || ((uintptr_t)q & 7) || ((uintptr_t)cache & 7) || ((uintptr_t)pooled & 7))
-    G2B_REFUSE("attn_pool_decode: query rows %d elements apart; q and the stores 8-byte aligned", q_stride);
+  if (q_stride < nh * HD || ((uintptr_t)cache & 15) || ((uintptr_t)pooled & 15))
+    G2B_REFUSE("attn_pool_decode: query rows %d elements apart; the stores 16-byte aligned", q_stride);
   const int group = nh / nkv;
   const long long tiles = (long long)nkv * ((group + GH - 1) / GH);
   if (tiles > 65535) G2B_REFUSE("attn_pool_decode: %lld head tiles are too many for one launch", tiles);
