@@ -1036,26 +1036,30 @@ extern "C" int g2b_scan_gates_step(const void *x, int dtype, int x_stride, const
 // Exponential gates held stable by a running maximum m (kept per slot and head, from 0):
 //   i = cap tanh((x_i + b_i) / cap);  f = logsigmoid(cap tanh((x_f + b_f) / cap));
 //   m' = max(f + m, i);  g = exp(f + m - m');  s = exp(i - m').
-// gates [T, 2H]: g, then s; m_out [T, H]: m' of every token.  A block walks one sequence's tokens
-// in tiles: the gates of a tile side by side, the chain of maxima by one thread per head, then the
-// exponentials side by side again; the chain depends on the tokens before in the sequence only.
+// gates [T, 2H]: g, then s; m_out [T, H]: m' of every token.  A block walks the tokens of one sequence
+// (and of some of its heads) in tiles: the gates of a tile side by side, the chain of maxima by one
+// thread per head, then the exponentials side by side again; the chain depends on the tokens before in
+// the sequence only.
 #define GATES_TILE 1024       // (token, head) pairs of a tile
 template <typename T>
 __global__ void __launch_bounds__(256)
 scan_gates_max_kernel(const T *__restrict__ xi, const T *__restrict__ xf, int x_stride, const float *__restrict__ bi,
                       const float *__restrict__ bf, float cap, int H, float *__restrict__ m_state,
                       const int *__restrict__ seq_slots, const int *__restrict__ seq_meta,
-                      float *__restrict__ gates, float *__restrict__ m_out) {
+                      float *__restrict__ gates, float *__restrict__ m_out, int heads_per_block) {
   pdl_launch();
   pdl_wait();
   __shared__ float si[GATES_TILE], sf[GATES_TILE], sm_new[GATES_TILE], sm_old[GATES_TILE];
   const int b = blockIdx.x;
   const int first_row = seq_meta ? seq_meta[4 * b + 0] : b, n = seq_meta ? seq_meta[4 * b + 1] : 1;
   const int slot = seq_meta ? seq_meta[4 * b + 3] : seq_slots[b];
-  const int tile = max(1, GATES_TILE / H);
   const float inv_cap = 1.f / cap;
-  for (int h0 = 0; h0 < H; h0 += GATES_TILE) {       // more heads than a tile holds: in turns
-    const int Hn = min(GATES_TILE, H - h0);
+  // a block takes `heads_per_block` heads (at most a tile's worth) of one sequence: few heads a block
+  // make the tiles long and the chains of many heads run side by side in other blocks
+  {
+    const int h0 = blockIdx.y * heads_per_block;
+    const int Hn = min(heads_per_block, H - h0);
+    const int tile = max(1, GATES_TILE / Hn);
     float m = threadIdx.x < Hn ? m_state[(size_t)slot * H + h0 + threadIdx.x] : 0.f;
     float m_hi[GATES_TILE / 256];                     // heads beyond the block's threads
 #pragma unroll
@@ -1127,12 +1131,16 @@ extern "C" int g2b_scan_gates_max(const void *xi, const void *xf, int dtype, int
   if (n_seqs <= 0 || H <= 0) return 0;
   if (!(cap > 0.f)) G2B_REFUSE("scan_gates_max: the gates' cap must be positive");
   if (!seq_meta && !seq_slots) G2B_REFUSE("scan_gates_max: neither the step's table of sequences nor their slots");
+  // prompts: a head a block (its chain is as long as the prompt); single tokens: a sequence's heads together
+  const int hb = seq_meta ? 1 : (H < GATES_TILE ? H : GATES_TILE);
+  const dim3 grid(n_seqs, (H + hb - 1) / hb);
+  if (grid.y > 65535) G2B_REFUSE("scan_gates_max: %d heads are too many for one launch", H);
   if (dtype == G2B_F32)
-    g2b_launch(scan_gates_max_kernel<float>, dim3(n_seqs), dim3(256), 0, stream, (const float *)xi, (const float *)xf,
-               x_stride, bi, bf, cap, H, m_state, seq_slots, seq_meta, gates, m_out);
+    g2b_launch(scan_gates_max_kernel<float>, grid, dim3(256), 0, stream, (const float *)xi, (const float *)xf,
+               x_stride, bi, bf, cap, H, m_state, seq_slots, seq_meta, gates, m_out, hb);
   else if (dtype == G2B_BF16)
-    g2b_launch(scan_gates_max_kernel<bf16>, dim3(n_seqs), dim3(256), 0, stream, (const bf16 *)xi, (const bf16 *)xf,
-               x_stride, bi, bf, cap, H, m_state, seq_slots, seq_meta, gates, m_out);
+    g2b_launch(scan_gates_max_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16 *)xi, (const bf16 *)xf,
+               x_stride, bi, bf, cap, H, m_state, seq_slots, seq_meta, gates, m_out, hb);
   else
     G2B_REFUSE("scan_gates_max: unknown dtype %d", dtype);
   return g2b_check_launch("scan_gates_max");
