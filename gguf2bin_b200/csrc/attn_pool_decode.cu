@@ -34,15 +34,17 @@ constexpr int TPR = HD / 8;                 // threads that cover a value row, 1
 constexpr int NS = THREADS / TPR;           // slices of a pass in the value phase
 static_assert(GH <= WARPS, "a warp per head in the softmax phase");
 
-// eight neighbouring bfloat16 as floats, fetched with one 16-byte load
-__device__ __forceinline__ void load8(const bf16 *p, float *f) {
-  const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p));
+// eight bfloat16 of one 16-byte load as floats
+__device__ __forceinline__ void unpack8(const uint4 &v, float *f) {
   const unsigned int w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
     const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w[e]));
     f[2 * e] = a.x, f[2 * e + 1] = a.y;
   }
+}
+__device__ __forceinline__ void load8(const bf16 *p, float *f) {
+  unpack8(__ldg(reinterpret_cast<const uint4 *>(p)), f);
 }
 }  // namespace
 
@@ -151,10 +153,19 @@ attn_pool_decode_kernel(const bf16 *__restrict__ q, bf16 *__restrict__ out, cons
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[g][e] *= corr;
     }
-#pragma unroll 4
-    for (int r = slice; r < n_here; r += NS) {
+    // every value row of the slice is asked for before the first is used: PASS / NS loads in flight
+    uint4 vv[PASS / NS];
+#pragma unroll
+    for (int it = 0; it < PASS / NS; ++it) {
+      const int r = slice + it * NS;
+      vv[it] = r < n_here ? __ldg(reinterpret_cast<const uint4 *>(vrow[r] + d8)) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int it = 0; it < PASS / NS; ++it) {
+      const int r = slice + it * NS;
+      if (r >= n_here) break;
       float vf[8];
-      load8(vrow[r] + d8, vf);
+      unpack8(vv[it], vf);
 #pragma unroll
       for (int g = 0; g < GH; ++g) {
         const float p = sc[g][r];                      // rows of heads that are not there hold zeros' scores: not written out
