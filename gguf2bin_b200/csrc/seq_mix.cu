@@ -1156,7 +1156,8 @@ extern "C" int g2b_scan_gates_max(const void *xi, const void *xf, int dtype, int
 //   gate_first:   y *= act(gate[j])
 //   y /= sqrt(mean over the element's group of `group` elements of y^2 + eps)
 //   y *= w[j mod w_len];  not gate_first: y *= act(gate[j])
-// act: 0 silu, 1 sigmoid.  One warp per (token, group).
+// act: 0 silu, 1 sigmoid.  One block per (token, group): a thread takes every 128th element, so that a
+// group of a few hundred elements is a few dependent rounds of loads and not sixteen.
 template <typename T>
 __global__ void __launch_bounds__(128)
 state_readout_kernel(const float *__restrict__ o, int T_tokens, int H, int V, int Vs, const float *__restrict__ m,
@@ -1165,10 +1166,10 @@ state_readout_kernel(const float *__restrict__ o, int T_tokens, int H, int V, in
                      const float *__restrict__ w, int w_len, T *__restrict__ out) {
   pdl_launch();
   pdl_wait();
+  __shared__ float part[4];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = H * V, groups = n / group;
-  const long long item = (long long)blockIdx.x * 4 + warp;
-  if (item >= (long long)T_tokens * groups) return;
+  const long long item = blockIdx.x;
   const int t = (int)(item / groups), j0 = (int)(item % groups) * group;
   const float *ot = o + (size_t)t * H * Vs;
   auto value = [&](int j) -> float {
@@ -1183,12 +1184,15 @@ state_readout_kernel(const float *__restrict__ o, int T_tokens, int H, int V, in
     return y;
   };
   float ss = 0.f;
-  for (int e = lane; e < group; e += 32) {
+  for (int e = threadIdx.x; e < group; e += 128) {
     const float y = value(j0 + e);
     ss = fmaf(y, y, ss);
   }
-  const float inv = 1.f / sqrtf(warp_sum(ss) / (float)group + eps);
-  for (int e = lane; e < group; e += 32) {
+  ss = warp_sum(ss);
+  if (lane == 0) part[warp] = ss;
+  __syncthreads();
+  const float inv = 1.f / sqrtf(((part[0] + part[1]) + (part[2] + part[3])) / (float)group + eps);
+  for (int e = threadIdx.x; e < group; e += 128) {
     const int j = j0 + e;
     float y = value(j) * inv;
     if (w) y *= w[j % w_len];
@@ -1209,7 +1213,9 @@ extern "C" int g2b_state_readout(const float *o, int T_tokens, int H, int V, int
   if (Vs < V || (m && Vs <= V)) G2B_REFUSE("state_readout: %d stored columns a head for %d outputs", Vs, V);
   if (w && w_len <= 0) G2B_REFUSE("state_readout: a weight of %d entries", w_len);
   if (skip_w && !x) G2B_REFUSE("state_readout: a skip weight without its input");
-  const unsigned blocks = (unsigned)(((long long)T_tokens * (H * V / group) + 3) / 4);
+  const long long items = (long long)T_tokens * (H * V / group);
+  if (items > 0x7fffffffLL) G2B_REFUSE("state_readout: %lld (token, group) pairs are too many for one launch", items);
+  const unsigned blocks = (unsigned)items;
   if (dtype == G2B_F32)
     g2b_launch(state_readout_kernel<float>, dim3(blocks), dim3(128), 0, stream, o, T_tokens, H, V, Vs, m, den_eps,
                (const float *)x, x_stride, skip_w, (const float *)gate, gate_stride, gate_act, gate_first, group, eps, w,
