@@ -447,6 +447,11 @@ struct Descent {
   float above;         // weight of admitted entries with key > key
 };
 
+// a weight in (0, 1] as a fixed-point number, and a sum of such numbers back as a float
+constexpr float FIXED_ONE = 1099511627776.f;                     // 2^40: sums of 2^24 weights fit in 64 bits
+__device__ __forceinline__ unsigned long long to_fixed(float w) { return (unsigned long long)(w * FIXED_ONE); }
+__device__ __forceinline__ float from_fixed(unsigned long long a) { return (float)a * (1.f / FIXED_ONE); }
+
 template <bool MASS>
 __device__ Descent radix_descent(const float *row, int V, float inv_temp, float mx,
                                  uint32_t bound_key, bool bounded, float target, float *hist) {
@@ -455,8 +460,12 @@ __device__ Descent radix_descent(const float *row, int V, float inv_temp, float 
   __shared__ float s_above;
   if (threadIdx.x == 0) { s_prefix = 0u; s_above = 0.f; }
   __syncthreads();
+  // Masses are added as 64-bit fixed-point numbers (FIXED_ONE to one): integer addition has no order,
+  // so a bucket's sum is the same bits whichever thread comes first, and the same row gives the same
+  // token in every launch.  (Counts are whole numbers in a float: exact as they are.)
+  __shared__ unsigned long long acc[256];
   for (int shift = 24; shift >= 0; shift -= 8) {
-    for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0.f;
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) { hist[i] = 0.f; acc[i] = 0ull; }
     __syncthreads();
     const uint32_t prefix = s_prefix;
     const uint32_t mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
@@ -465,10 +474,14 @@ __device__ Descent radix_descent(const float *row, int V, float inv_temp, float 
       const uint32_t k = order_key(v);
       if (bounded && k < bound_key) return;        // below the kept set
       if ((k & mask) != (prefix & mask)) return;
-      const float w = MASS ? expf(v - mx) : 1.f;
-      atomicAdd(&hist[(k >> shift) & 0xffu], w);
+      if (MASS) atomicAdd(&acc[(k >> shift) & 0xffu], to_fixed(expf(v - mx)));
+      else atomicAdd(&hist[(k >> shift) & 0xffu], 1.f);
     });
     __syncthreads();
+    if (MASS) {
+      for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = from_fixed(acc[i]);
+      __syncthreads();
+    }
     if (threadIdx.x == 0) {
       float run = s_above;
       int chosen = -1, last = 0;
@@ -569,7 +582,7 @@ __device__ float admitted_mass(const float *row, int V, float inv_temp, float mx
 // the whole row.  When neither gives a list that fits (thousands of logits sharing 22 bits, a
 // top_p that needs more than the list holds) the caller takes the descents over the whole row.
 constexpr int LIST_CAP = 2048;
-struct ShortList {
+struct alignas(16) ShortList {
   uint32_t key[LIST_CAP];
   int idx[LIST_CAP];
   float e[LIST_CAP];
@@ -1014,14 +1027,21 @@ __device__ int pick_by_buckets(const float *row, int V, float inv_temp, float to
   int *cnt = L.hist;
   float mx;
   block_argmax(row, V, inv_temp, &mx);
-  for (int i = threadIdx.x; i < N_BUCKETS; i += blockDim.x) { mass[i] = 0.f; cnt[i] = 0; }
+  // the masses are added in fixed point (see radix_descent) in the list's key and index arrays, which
+  // nobody uses before the first bucket is listed
+  static_assert(offsetof(ShortList, idx) == sizeof(uint32_t) * LIST_CAP && sizeof(unsigned long long) == 8,
+                "keys and indices lie side by side: 2,048 sums of 64 bits");
+  unsigned long long *acc = reinterpret_cast<unsigned long long *>(L.key);
+  for (int i = threadIdx.x; i < N_BUCKETS; i += blockDim.x) { acc[i] = 0ull; cnt[i] = 0; }
   __syncthreads();
   scan_row(row, V, [&](int, float x) {
     const float v = x * inv_temp;
     const int b = bucket_of(v, mx);
-    atomicAdd(&mass[b], expf(v - mx));
+    atomicAdd(&acc[b], to_fixed(expf(v - mx)));
     atomicAdd(&cnt[b], 1);
   });
+  __syncthreads();
+  for (int i = threadIdx.x; i < N_BUCKETS; i += blockDim.x) mass[i] = from_fixed(acc[i]);
   __syncthreads();
   if (threadIdx.x < 32) {
     // cumulative sums in bucket order: lane l owns the 64 buckets from 64 l
