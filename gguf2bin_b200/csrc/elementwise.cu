@@ -774,3 +774,139 @@ extern "C" int g2b_rewind_step(int *tok_pos, int n, int *seq_state, int words, c
              undo_draw, undo_recent);
   return g2b_check_launch("rewind_step");
 }
+
+// ---------------------------------------------------------------------------
+// a norm without statistics, sublayer results joined with a weight per channel,
+// and the squared rectifier
+// ---------------------------------------------------------------------------
+// out[r] = tanh(alpha x[row_r]) * w + b: nothing is summed over the row, so a thread takes four
+// neighbours of any row; alpha is one number, read from the device.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+tanh_norm_kernel(const float *__restrict__ x, const float *__restrict__ alpha, const float *__restrict__ w,
+                 const float *__restrict__ b, const int *__restrict__ rows, TO *__restrict__ out, int n_rows, int H) {
+  pdl_launch();
+  pdl_wait();
+  const float a = alpha[0];
+  const long long total = (long long)n_rows * H;
+  if ((H & 3) == 0) {
+    const long long i = ((long long)blockIdx.x * 256 + threadIdx.x) * 4;
+    if (i >= total) return;
+    const int r = (int)(i / H), k = (int)(i % H);
+    const float4 v = *reinterpret_cast<const float4 *>(x + (size_t)(rows ? rows[r] : r) * H + k);
+    const float4 g = *reinterpret_cast<const float4 *>(w + k), c = *reinterpret_cast<const float4 *>(b + k);
+    store4(out + i, fmaf(tanhf(a * v.x), g.x, c.x), fmaf(tanhf(a * v.y), g.y, c.y), fmaf(tanhf(a * v.z), g.z, c.z),
+           fmaf(tanhf(a * v.w), g.w, c.w));
+    return;
+  }
+  for (int j = 0; j < 4; ++j) {
+    const long long i = ((long long)blockIdx.x * 256 + threadIdx.x) * 4 + j;
+    if (i >= total) return;
+    const int r = (int)(i / H), k = (int)(i % H);
+    out[i] = from_f32<TO>(fmaf(tanhf(a * x[(size_t)(rows ? rows[r] : r) * H + k]), w[k], b[k]));
+  }
+}
+
+extern "C" int g2b_tanh_norm(const float *x, const float *alpha, const float *w, const float *b, const int *rows,
+                             int n_rows, int H, void *out, int out_dtype, cudaStream_t stream) {
+  if (n_rows <= 0 || H <= 0) return 0;
+  const long long quads = ((long long)n_rows * H + 3) / 4;
+  const unsigned blocks = (unsigned)((quads + 255) / 256);
+  if (out_dtype == G2B_F32)
+    g2b_launch(tanh_norm_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, alpha, w, b, rows, (float *)out, n_rows, H);
+  else if (out_dtype == G2B_BF16)
+    g2b_launch(tanh_norm_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, x, alpha, w, b, rows, (bf16 *)out, n_rows, H);
+  else
+    G2B_REFUSE("tanh_norm: unknown dtype %d", out_dtype);
+  return g2b_check_launch("tanh_norm");
+}
+
+// x += y1 * s1 + y2 * s2 (s: one number per channel; y2 may be absent), all float
+__global__ void __launch_bounds__(256)
+scaled_join_kernel(float *__restrict__ x, const float *__restrict__ y1, const float *__restrict__ s1,
+                   const float *__restrict__ y2, const float *__restrict__ s2, long long total, int H) {
+  pdl_launch();
+  pdl_wait();
+  if ((H & 3) == 0) {
+    const long long i = ((long long)blockIdx.x * 256 + threadIdx.x) * 4;
+    if (i >= total) return;
+    const int k = (int)(i % H);
+    float4 v = *reinterpret_cast<float4 *>(x + i);
+    const float4 a = *reinterpret_cast<const float4 *>(y1 + i), ga = *reinterpret_cast<const float4 *>(s1 + k);
+    float4 add = make_float4(a.x * ga.x, a.y * ga.y, a.z * ga.z, a.w * ga.w);
+    if (y2) {
+      const float4 c = *reinterpret_cast<const float4 *>(y2 + i), gc = *reinterpret_cast<const float4 *>(s2 + k);
+      add.x = fmaf(c.x, gc.x, add.x); add.y = fmaf(c.y, gc.y, add.y);
+      add.z = fmaf(c.z, gc.z, add.z); add.w = fmaf(c.w, gc.w, add.w);
+    }
+    v.x += add.x; v.y += add.y; v.z += add.z; v.w += add.w;
+    *reinterpret_cast<float4 *>(x + i) = v;
+    return;
+  }
+  for (int j = 0; j < 4; ++j) {
+    const long long i = ((long long)blockIdx.x * 256 + threadIdx.x) * 4 + j;
+    if (i >= total) return;
+    const int k = (int)(i % H);
+    float add = y1[i] * s1[k];
+    if (y2) add = fmaf(y2[i], s2[k], add);
+    x[i] += add;
+  }
+}
+
+extern "C" int g2b_scaled_join(float *x, const float *y1, const float *s1, const float *y2, const float *s2,
+                               int n_rows, int H, cudaStream_t stream) {
+  if (n_rows <= 0 || H <= 0) return 0;
+  const long long total = (long long)n_rows * H, quads = (total + 3) / 4;
+  g2b_launch(scaled_join_kernel, dim3((unsigned)((quads + 255) / 256)), dim3(256), 0, stream, x, y1, s1, y2, s2, total, H);
+  return g2b_check_launch("scaled_join");
+}
+
+// out = max(z, 0)^2; z rows may lie apart (columns of a wider product's output)
+template <typename T>
+__global__ void __launch_bounds__(256)
+relu2_kernel(const T *__restrict__ z, int z_stride, T *__restrict__ out, long long total, int F) {
+  pdl_launch();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= total) return;
+  const float v = fmaxf(to_f32(z[(size_t)(i / F) * z_stride + (i % F)]), 0.f);
+  out[i] = from_f32<T>(v * v);
+}
+
+__global__ void __launch_bounds__(256)
+relu2x8_kernel(const bf16 *__restrict__ z, int z_stride, bf16 *__restrict__ out, long long total8, int F) {
+  pdl_launch();
+  pdl_wait();
+  const long long i8 = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i8 >= total8) return;
+  const long long i = i8 * 8;
+  const uint4 raw = *reinterpret_cast<const uint4 *>(z + (size_t)(i / F) * z_stride + (i % F));
+  const __nv_bfloat162 *in = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+  uint4 o;
+  __nv_bfloat162 *op = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float2 f = __bfloat1622float2(in[j]);
+    f.x = fmaxf(f.x, 0.f); f.y = fmaxf(f.y, 0.f);
+    op[j] = __floats2bfloat162_rn(f.x * f.x, f.y * f.y);
+  }
+  *reinterpret_cast<uint4 *>(out + i) = o;
+}
+
+extern "C" int g2b_relu2(const void *z, int z_stride, int dtype, int T_tokens, int F, void *out, cudaStream_t stream) {
+  if (T_tokens <= 0 || F <= 0) return 0;
+  const long long total = (long long)T_tokens * F;
+  if (dtype == G2B_BF16 && F % 8 == 0 && z_stride % 8 == 0 && !(((uintptr_t)z | (uintptr_t)out) & 15)) {
+    g2b_launch(relu2x8_kernel, dim3((unsigned)((total / 8 + 255) / 256)), dim3(256), 0, stream, (const bf16 *)z, z_stride,
+               (bf16 *)out, total / 8, F);
+    return g2b_check_launch("relu2");
+  }
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == G2B_F32)
+    g2b_launch(relu2_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float *)z, z_stride, (float *)out, total, F);
+  else if (dtype == G2B_BF16)
+    g2b_launch(relu2_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16 *)z, z_stride, (bf16 *)out, total, F);
+  else
+    G2B_REFUSE("relu2: unknown dtype %d", dtype);
+  return g2b_check_launch("relu2");
+}

@@ -1,6 +1,7 @@
 // A routed feed-forward: every token goes through `top` of a layer's small feed-forwards.
 //
-//   moe_route    scores s = softmax(z) over all experts in 32-bit; the `top` largest of s + c
+//   moe_route    scores s = softmax(z) over all experts (or sigmoid(z), each by itself) in 32-bit;
+//                optionally only the experts of the best groups of neighbours stay eligible; the `top` largest of s + c
 //                (c: a stored correction that steers the choice only) are chosen, ties to the
 //                lower index; the weights are the chosen experts' s as they are, or divided by
 //                their sum; then times `scale`.  idx [T, top], weight [T, top].
@@ -69,33 +70,73 @@ extern "C" int g2b_moe_gather(const void *A, int dtype, int a_stride, const int 
 // router
 // ---------------------------------------------------------------------------
 #define ROUTE_WARPS 4
+// `sigmoid`: the scores are sigmoids of the logits, each by itself, instead of a softmax over all.
+// `groups` > 1: the experts form that many equal groups of neighbours; a group's score is the sum of its
+// two largest scores (of score + correction); only experts of the `keep` best groups can be chosen.
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const float *__restrict__ z, const float *__restrict__ correction, int T, int N, int top,
-                 int renormalise, int *__restrict__ idx, float *__restrict__ weight, float scale) {
+                 int renormalise, int *__restrict__ idx, float *__restrict__ weight, float scale, int sigmoid,
+                 int groups, int keep) {
   pdl_launch();
   pdl_wait();
-  extern __shared__ float sm[];                 // per warp: s [N], pick [N]
+  extern __shared__ float sm[];                 // per warp: s [N], pick [N], group scores [groups]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * ROUTE_WARPS + warp;
   if (t >= T) return;
-  float *s = sm + (size_t)warp * 2 * N, *pick = s + N;
+  float *s = sm + (size_t)warp * (2 * N + groups), *pick = s + N, *gs = pick + N;
   const float *zr = z + (size_t)t * N;
-  float m = -INFINITY;
-  for (int j = lane; j < N; j += 32) m = fmaxf(m, zr[j]);
-  m = warp_max(m);
-  float sum = 0.f;
-  for (int j = lane; j < N; j += 32) {
-    const float e = expf(zr[j] - m);
-    s[j] = e;
-    sum += e;
-  }
-  sum = warp_sum(sum);
-  const float inv = 1.f / sum;
-  for (int j = lane; j < N; j += 32) {
-    s[j] *= inv;
-    pick[j] = s[j] + (correction ? correction[j] : 0.f);
+  if (sigmoid) {
+    for (int j = lane; j < N; j += 32) {
+      s[j] = 1.f / (1.f + expf(-zr[j]));
+      pick[j] = s[j] + (correction ? correction[j] : 0.f);
+    }
+  } else {
+    float m = -INFINITY;
+    for (int j = lane; j < N; j += 32) m = fmaxf(m, zr[j]);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int j = lane; j < N; j += 32) {
+      const float e = expf(zr[j] - m);
+      s[j] = e;
+      sum += e;
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;
+    for (int j = lane; j < N; j += 32) {
+      s[j] *= inv;
+      pick[j] = s[j] + (correction ? correction[j] : 0.f);
+    }
   }
   __syncwarp();
+  if (groups > 1) {
+    const int per = N / groups;
+    for (int g = lane; g < groups; g += 32) {     // the sum of a group's two best
+      float a = -INFINITY, b = -INFINITY;
+      for (int j = g * per; j < (g + 1) * per; ++j) {
+        const float v = pick[j];
+        if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+      }
+      gs[g] = per > 1 ? a + b : a;
+    }
+    __syncwarp();
+    for (int r = 0; r < keep; ++r) {              // the best groups, one after another; ties to the lower index
+      float best = -INFINITY;
+      int at = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32)
+        if (gs[g] > best) { best = gs[g]; at = g; }
+      for (int off = 16; off > 0; off >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, off);
+        if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+      }
+      if (at >= groups) break;                    // nothing left (NaN scores): every lane agrees
+      if (lane == 0) gs[at] = -INFINITY;          // taken: marked by the value no score has
+      __syncwarp();
+    }
+    for (int j = lane; j < N; j += 32)
+      if (gs[j / per] != -INFINITY) pick[j] = -INFINITY;      // its group was not kept
+    __syncwarp();
+  }
   float chosen_sum = 0.f;
   for (int r = 0; r < top; ++r) {
     float best = -INFINITY;
@@ -117,17 +158,22 @@ moe_route_kernel(const float *__restrict__ z, const float *__restrict__ correcti
     __syncwarp();
   }
   if (renormalise && lane == 0)
-    for (int r = 0; r < top; ++r) weight[(size_t)t * top + r] = weight[(size_t)t * top + r] / chosen_sum * scale;
+    for (int r = 0; r < top; ++r)
+      weight[(size_t)t * top + r] = weight[(size_t)t * top + r] / (chosen_sum + 1e-20f) * scale;
 }
 
 extern "C" int g2b_moe_route(const float *z, const float *correction, int T, int N, int top, int renormalise,
-                             int *idx, float *weight, float scale, cudaStream_t stream) {
+                             int *idx, float *weight, float scale, int sigmoid, int groups, int keep,
+                             cudaStream_t stream) {
   if (T <= 0) return 0;
   if (top < 1 || top > N) G2B_REFUSE("moe_route: %d choices among %d experts", top, N);
-  const size_t smem = (size_t)ROUTE_WARPS * 2 * N * sizeof(float);
+  if (groups < 1) groups = 1;
+  if (groups > 1 && (N % groups || keep < 1 || keep > groups || top > keep * (N / groups)))
+    G2B_REFUSE("moe_route: %d experts in %d groups of which %d are kept, for %d choices", N, groups, keep, top);
+  const size_t smem = (size_t)ROUTE_WARPS * (2 * N + groups) * sizeof(float);
   if (smem > 48 * 1024) G2B_REFUSE("moe_route: %d experts are more than a block's shared memory holds", N);
   g2b_launch(moe_route_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, stream, z,
-             correction, T, N, top, renormalise, idx, weight, scale);
+             correction, T, N, top, renormalise, idx, weight, scale, sigmoid, groups, keep);
   return g2b_check_launch("moe_route");
 }
 

@@ -7,7 +7,14 @@
 //                         at once, times a weight; rotation of the first `rot` entries of every
 //                         head, pairs (i, i + rot/2) or (2i, 2i + 1); q out, k and v into the
 //                         layer's pages.  Key and value heads may differ in size: both are
-//                         stored zero-filled to the larger, and so is q.
+//                         stored zero-filled to the larger, and so is q.  Options: the norm per
+//                         head instead (a weight of one head's size), every head of q and k
+//                         divided by its root mean square after the rotation, fewer value heads
+//                         than key heads, and no keys and values at all (q only).
+//   selective_scan        a state S [channels, N] per sequence with a decay per entry:
+//                         S[c, n] = exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n, y_c = sum_n S[c, n] C_n,
+//                         dt = softplus(. + bias); out = (y + D x) silu(z) times a constant
+//   diff_combine          two attention maps per head: (a1 - lambda a2) / rms, times a constant
 //   rotate_heads          the rotation alone, in place, then times a constant
 //   short_conv            y_t = act(sum_j w[j, c] x_{t - taps + 1 + j}[c]); rows before the step's
 //                         first come from a ring of `taps` rows per slot indexed by position mod
@@ -60,10 +67,11 @@ proj_norm_rope_cache_kernel(const T *__restrict__ qkv, int row_stride, const flo
                             const float *__restrict__ k_w, float eps, const float2 *__restrict__ rope,
                             int rot, int interleaved, const int *__restrict__ tok_pos,
                             const int *__restrict__ tok_seq, const int *__restrict__ page_table, int P,
-                            T *__restrict__ cache, int page_size, T *__restrict__ q_out, float v_norm_eps) {
+                            T *__restrict__ cache, int page_size, T *__restrict__ q_out, float v_norm_eps,
+                            int norm_per_head, float unit_eps, int nvh) {
   pdl_launch();
   pdl_wait();
-  extern __shared__ float sm[];                     // q [nh*D], k [nkv*D], one factor per value head [nkv]
+  extern __shared__ float sm[];                     // q [nh*D], k [nkv*D], one factor per value head [nvh]
   __shared__ float scratch[32];
   const int t = blockIdx.x;
   const int nq = nh * D, nk = nkv * D;
@@ -76,27 +84,49 @@ proj_norm_rope_cache_kernel(const T *__restrict__ qkv, int row_stride, const flo
     sm[j] = v;
     if (j < nq) sq = fmaf(v, v, sq); else sk = fmaf(v, v, sk);
   }
-  if (q_w) sq = block_sum(sq, scratch);
-  if (k_w) sk = block_sum(sk, scratch);
+  const bool whole = !norm_per_head;
+  if (q_w && whole) sq = block_sum(sq, scratch);
+  if (k_w && whole) sk = block_sum(sk, scratch);
   __syncthreads();
-  if (q_w) {
+  if (q_w && whole) {
     const float inv = 1.f / sqrtf(sq / (float)nq + eps);
     for (int j = threadIdx.x; j < nq; j += blockDim.x) xq[j] = xq[j] * inv * q_w[j];
   }
-  if (k_w) {
+  if (k_w && whole && nk) {
     const float inv = 1.f / sqrtf(sk / (float)nk + eps);
     for (int j = threadIdx.x; j < nk; j += blockDim.x) xk[j] = xk[j] * inv * k_w[j];
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
-  if (rope) {
-    const float2 *cs = rope + (size_t)t * (rot >> 1);
-    for (int h = warp; h < nh + nkv; h += n_warps) rotate_in_place(sm + (size_t)h * D, cs, rot, interleaved, lane);
+  if (rope || norm_per_head || unit_eps > 0.f) {
+    // a warp per head: norm with a weight over the head, rotation, division by the root mean square
+    const float2 *cs = rope ? rope + (size_t)t * (rot >> 1) : nullptr;
+    for (int h = warp; h < nh + nkv; h += n_warps) {
+      float *x = sm + (size_t)h * D;
+      const float *w = h < nh ? q_w : k_w;
+      if (norm_per_head && w) {
+        float ss = 0.f;
+        for (int d = lane; d < D; d += 32) ss = fmaf(x[d], x[d], ss);
+        const float inv = 1.f / sqrtf(warp_sum(ss) / (float)D + eps);
+        for (int d = lane; d < D; d += 32) x[d] = x[d] * inv * w[d];
+        __syncwarp();
+      }
+      if (cs) {
+        rotate_in_place(x, cs, rot, interleaved, lane);
+        __syncwarp();
+      }
+      if (unit_eps > 0.f) {
+        float ss = 0.f;
+        for (int d = lane; d < D; d += 32) ss = fmaf(x[d], x[d], ss);
+        const float inv = 1.f / sqrtf(warp_sum(ss) / (float)D + unit_eps);
+        for (int d = lane; d < D; d += 32) x[d] *= inv;
+      }
+    }
     __syncthreads();
   }
   float *v_inv = sm + nq + nk;                      // value heads divided by their root mean square
   if (v_norm_eps > 0.f) {
-    for (int h = warp; h < nkv; h += n_warps) {
+    for (int h = warp; h < nvh; h += n_warps) {
       float ss = 0.f;
       for (int d = lane; d < V; d += 32) {
         const float v = to_f32(src[nq + nk + h * V + d]) + (bias ? bias[nq + nk + h * V + d] : 0.f);
@@ -107,18 +137,20 @@ proj_norm_rope_cache_kernel(const T *__restrict__ qkv, int row_stride, const flo
     }
     __syncthreads();
   }
-  const int pos = tok_pos[t];
-  const int page = page_table[(size_t)tok_seq[t] * P + pos / page_size];
-  const int in_page = pos % page_size;
   for (int j = threadIdx.x; j < nh * hd; j += blockDim.x) {
     const int h = j / hd, d = j % hd;
     q_out[(size_t)t * nh * hd + j] = from_f32<T>(d < D ? xq[h * D + d] : 0.f);
   }
+  if (nkv <= 0) return;                             // a layer that reads another layer's keys and values
+  const int pos = tok_pos[t];
+  const int page = page_table[(size_t)tok_seq[t] * P + pos / page_size];
+  const int in_page = pos % page_size;
   for (int j = threadIdx.x; j < nkv * hd; j += blockDim.x) {
     const int h = j / hd, d = j % hd;
     T *kd = cache + ((((size_t)page * 2 + 0) * nkv + h) * page_size + in_page) * hd;
-    T *vd = cache + ((((size_t)page * 2 + 1) * nkv + h) * page_size + in_page) * hd;
     kd[d] = from_f32<T>(d < D ? xk[h * D + d] : 0.f);
+    if (h >= nvh) continue;                         // fewer value heads than key heads: the rest of the panel is unused
+    T *vd = cache + ((((size_t)page * 2 + 1) * nkv + h) * page_size + in_page) * hd;
     float v = d < V ? to_f32(src[nq + nk + h * V + d]) + (bias ? bias[nq + nk + h * V + d] : 0.f) : 0.f;
     if (v_norm_eps > 0.f) v *= v_inv[h];
     vd[d] = from_f32<T>(v);
@@ -130,9 +162,11 @@ extern "C" int g2b_proj_norm_rope_cache(const void *qkv, int dtype, int row_stri
                                         const float *k_w, float eps, const float *rope, int rot, int interleaved,
                                         const int *tok_pos, const int *tok_seq, const int *page_table, int P,
                                         void *cache, int page_size, void *q_out, float v_norm_eps,
-                                        cudaStream_t stream) {
+                                        int norm_per_head, float unit_eps, int nvh, cudaStream_t stream) {
   if (T_tokens <= 0) return 0;
   if (rope && (rot <= 0 || rot > D || (rot & 1))) G2B_REFUSE("proj_norm_rope_cache: %d rotated entries of a head of %d", rot, D);
+  if (nkv < 0 || nvh < 0 || nvh > nkv) G2B_REFUSE("proj_norm_rope_cache: %d value heads beside %d key heads", nvh, nkv);
+  if (nkv > 0 && !cache) G2B_REFUSE("proj_norm_rope_cache: keys without pages to write them to");
   const size_t smem = ((size_t)(nh + nkv) * D + nkv) * sizeof(float);
   if (smem > 200 * 1024) G2B_REFUSE("proj_norm_rope_cache: q and k of %d entries do not fit a block's shared memory", (nh + nkv) * D);
   if (dtype == G2B_F32) {
@@ -140,13 +174,13 @@ extern "C" int g2b_proj_norm_rope_cache(const void *qkv, int dtype, int row_stri
     if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     g2b_launch(k, dim3(T_tokens), dim3(256), smem, stream, (const float *)qkv, row_stride, bias, nh, nkv, D, V, q_w, k_w,
                eps, (const float2 *)rope, rot, interleaved, tok_pos, tok_seq, page_table, P, (float *)cache, page_size,
-               (float *)q_out, v_norm_eps);
+               (float *)q_out, v_norm_eps, norm_per_head, unit_eps, nvh);
   } else if (dtype == G2B_BF16) {
     auto k = proj_norm_rope_cache_kernel<bf16>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     g2b_launch(k, dim3(T_tokens), dim3(256), smem, stream, (const bf16 *)qkv, row_stride, bias, nh, nkv, D, V, q_w, k_w,
                eps, (const float2 *)rope, rot, interleaved, tok_pos, tok_seq, page_table, P, (bf16 *)cache, page_size,
-               (bf16 *)q_out, v_norm_eps);
+               (bf16 *)q_out, v_norm_eps, norm_per_head, unit_eps, nvh);
   } else {
     G2B_REFUSE("proj_norm_rope_cache: unknown dtype %d", dtype);
   }
@@ -1284,4 +1318,173 @@ extern "C" int g2b_pool_update(const void *cache, void *pooled, int dtype, const
   else
     G2B_REFUSE("pool_update: unknown dtype %d", dtype);
   return g2b_check_launch("pool_update");
+}
+
+// ---------------------------------------------------------------------------
+// selective scan: a decay per state entry
+// ---------------------------------------------------------------------------
+// A channel's N state entries are held by L lanes of one warp, P = ceil(N / L) <= MAXP each: lane l
+// holds entries l, l + L, ...  A block owns SEL_THREADS / L channels of one sequence and walks the
+// step's tokens in order, SEL_TILE at a time: a tile's B and C rows, step sizes (softplus applied)
+// and inputs are staged in shared memory by the whole block, then every lane runs its entries
+// through the tile; a channel's read-outs are summed over its lanes by shuffles (an order that
+// depends on N and L only) and leave through shared memory with the skip, the gate and the scale
+// applied.  What a token gets depends on the tokens before it in its sequence only.
+#define SEL_THREADS 128
+#define SEL_TILE 16
+
+template <typename T, int MAXP>
+__global__ void __launch_bounds__(SEL_THREADS)
+selective_scan_kernel(const T *__restrict__ x, int x_stride, const float *__restrict__ dt_raw, int dt_stride,
+                      const float *__restrict__ dt_bias, const T *__restrict__ bc, int bc_stride,
+                      const float *__restrict__ A, const float *__restrict__ skip, const T *__restrict__ z,
+                      int z_stride, float *__restrict__ state, const int *__restrict__ seq_slots,
+                      const int *__restrict__ seq_meta, int inner, int N, int L, float out_scale,
+                      T *__restrict__ out, int out_stride) {
+  pdl_launch();
+  pdl_wait();
+  extern __shared__ float sm[];
+  const int cpb = SEL_THREADS / L;                       // channels of this block
+  float *bcs = sm;                                       // [SEL_TILE][2N]
+  float *dts = bcs + (size_t)SEL_TILE * 2 * N;           // [SEL_TILE][cpb]
+  float *xs = dts + SEL_TILE * cpb;                      // [SEL_TILE][cpb]
+  float *ys = xs + SEL_TILE * cpb;                       // [SEL_TILE][cpb]
+  const int b = blockIdx.y;
+  const int first = seq_meta ? seq_meta[4 * b + 0] : b;
+  const int n_tok = seq_meta ? seq_meta[4 * b + 1] : 1;
+  const int slot = seq_meta ? seq_meta[4 * b + 3] : seq_slots[b];
+  const int c0 = blockIdx.x * cpb;
+  const int cl = threadIdx.x / L, sub = threadIdx.x % L;
+  const int c = c0 + cl;
+  const bool live = c < inner;
+  float S[MAXP], a[MAXP];
+  float *my_state = state + ((size_t)slot * inner + (live ? c : 0)) * N;
+#pragma unroll
+  for (int i = 0; i < MAXP; ++i) {
+    const int n = sub + L * i;
+    const bool has = live && n < N;
+    S[i] = has ? my_state[n] : 0.f;
+    a[i] = has ? A[(size_t)c * N + n] : 0.f;
+  }
+  for (int t0 = 0; t0 < n_tok; t0 += SEL_TILE) {
+    const int here = min(SEL_TILE, n_tok - t0);
+    __syncthreads();                                     // the tile before has left shared memory
+    for (int i = threadIdx.x; i < here * 2 * N; i += SEL_THREADS) {
+      const int r = i / (2 * N), j = i % (2 * N);
+      bcs[i] = to_f32(bc[(size_t)(first + t0 + r) * bc_stride + j]);
+    }
+    for (int i = threadIdx.x; i < here * cpb; i += SEL_THREADS) {
+      const int r = i / cpb, ch = c0 + i % cpb;
+      if (ch < inner) {
+        const size_t row = (size_t)(first + t0 + r);
+        dts[i] = softplus_f(dt_raw[row * dt_stride + ch] + dt_bias[ch]);
+        xs[i] = to_f32(x[row * x_stride + ch]);
+      } else {
+        dts[i] = xs[i] = 0.f;
+      }
+    }
+    __syncthreads();
+    for (int r = 0; r < here; ++r) {                     // lanes beyond the last channel run along on zeros
+      const float dt = dts[r * cpb + cl], dx = dt * xs[r * cpb + cl];
+      const float *Bs = bcs + (size_t)r * 2 * N, *Cs = Bs + N;
+      float y = 0.f;
+#pragma unroll
+      for (int i = 0; i < MAXP; ++i) {
+        const int n = sub + L * i;
+        if (n < N) {
+          S[i] = fmaf(expf(dt * a[i]), S[i], dx * Bs[n]);
+          y = fmaf(S[i], Cs[n], y);
+        }
+      }
+      for (int o = L >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o, 32);
+      if (sub == 0) ys[r * cpb + cl] = y;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < here * cpb; i += SEL_THREADS) {
+      const int r = i / cpb, ch = c0 + i % cpb;
+      if (ch < inner) {
+        const size_t row = (size_t)(first + t0 + r);
+        const float g = to_f32(z[row * z_stride + ch]);
+        out[row * out_stride + ch] = from_f32<T>((ys[i] + skip[ch] * xs[i]) * silu_f(g) * out_scale);
+      }
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < MAXP; ++i) {
+      const int n = sub + L * i;
+      if (n < N) my_state[n] = S[i];
+    }
+  }
+}
+
+extern "C" int g2b_selective_scan(const void *x, int dtype, int x_stride, const float *dt_raw, int dt_stride,
+                                  const float *dt_bias, const void *bc, int bc_stride, const float *A,
+                                  const float *skip, const void *z, int z_stride, float *state,
+                                  const int *seq_slots, const int *seq_meta, int T_tokens, int n_seqs, int inner,
+                                  int N, float out_scale, void *out, int out_stride, cudaStream_t stream) {
+  if (T_tokens <= 0 || inner <= 0) return 0;
+  if (N <= 0 || N > 256) G2B_REFUSE("selective_scan: a state of %d entries a channel (1..256)", N);
+  const int seqs = seq_meta ? n_seqs : T_tokens;
+  if (seqs > 65535) G2B_REFUSE("selective_scan: %d sequences are too many for one launch", seqs);
+  const int maxp = N > 128 ? 8 : 4;
+  int L = 1;
+  while (L * maxp < N) L <<= 1;                           // lanes a channel: 1 .. 32
+  const int cpb = SEL_THREADS / L;
+  const dim3 grid((inner + cpb - 1) / cpb, seqs);
+  const size_t smem = ((size_t)SEL_TILE * 2 * N + 3 * (size_t)SEL_TILE * cpb) * sizeof(float);
+#define G2B_SEL(TYPE, MAXP)                                                                                        \
+  g2b_launch(selective_scan_kernel<TYPE, MAXP>, grid, dim3(SEL_THREADS), smem, stream, (const TYPE *)x, x_stride,  \
+             dt_raw, dt_stride, dt_bias, (const TYPE *)bc, bc_stride, A, skip, (const TYPE *)z, z_stride, state,   \
+             seq_slots, seq_meta, inner, N, L, out_scale, (TYPE *)out, out_stride)
+  if (dtype == G2B_F32) {
+    if (maxp == 4) G2B_SEL(float, 4); else G2B_SEL(float, 8);
+  } else if (dtype == G2B_BF16) {
+    if (maxp == 4) G2B_SEL(bf16, 4); else G2B_SEL(bf16, 8);
+  } else {
+    G2B_REFUSE("selective_scan: unknown dtype %d", dtype);
+  }
+#undef G2B_SEL
+  return g2b_check_launch("selective_scan");
+}
+
+// ---------------------------------------------------------------------------
+// two attention maps per head, the second subtracted
+// ---------------------------------------------------------------------------
+// a [T, 2 * heads * hd]: the first map's heads, then the second's (heads padded to hd entries, V in
+// use); out[t, h] = (a1 - lambda a2) / sqrt(mean((a1 - lambda a2)^2) + eps) * post, heads unpadded.
+template <typename T>
+__global__ void __launch_bounds__(128)
+diff_combine_kernel(const T *__restrict__ a, int heads, int hd, int V, float lambda, float eps, float post,
+                    T *__restrict__ out, int n_items) {
+  pdl_launch();
+  pdl_wait();
+  const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (item >= n_items) return;
+  const int t = item / heads, h = item % heads;
+  const T *a1 = a + ((size_t)t * 2 * heads + h) * hd, *a2 = a1 + (size_t)heads * hd;
+  float ss = 0.f;
+  for (int d = lane; d < V; d += 32) {
+    const float o = to_f32(a1[d]) - lambda * to_f32(a2[d]);
+    ss = fmaf(o, o, ss);
+  }
+  const float inv = post / sqrtf(warp_sum(ss) / (float)V + eps);
+  T *op = out + ((size_t)t * heads + h) * V;
+  for (int d = lane; d < V; d += 32) op[d] = from_f32<T>((to_f32(a1[d]) - lambda * to_f32(a2[d])) * inv);
+}
+
+extern "C" int g2b_diff_combine(const void *a, int dtype, int T_tokens, int heads, int hd, int V, float lambda,
+                                float eps, float post, void *out, cudaStream_t stream) {
+  if (T_tokens <= 0) return 0;
+  if (V <= 0 || V > hd) G2B_REFUSE("diff_combine: %d values of a head stored in %d", V, hd);
+  const int items = T_tokens * heads;
+  if (dtype == G2B_F32)
+    g2b_launch(diff_combine_kernel<float>, dim3((items + 3) / 4), dim3(128), 0, stream, (const float *)a, heads, hd, V,
+               lambda, eps, post, (float *)out, items);
+  else if (dtype == G2B_BF16)
+    g2b_launch(diff_combine_kernel<bf16>, dim3((items + 3) / 4), dim3(128), 0, stream, (const bf16 *)a, heads, hd, V,
+               lambda, eps, post, (bf16 *)out, items);
+  else
+    G2B_REFUSE("diff_combine: unknown dtype %d", dtype);
+  return g2b_check_launch("diff_combine");
 }

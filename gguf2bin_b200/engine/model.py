@@ -19,6 +19,7 @@ from ..config.specs import ConfigError
 from ..csrc.build import _log
 from ..parts import block_class, embedding_class, head_class, norm_class
 from ..parts.base import StepContext
+from ..parts.norms import bind_norm
 from ..weights.loader import load_weights
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
@@ -101,7 +102,7 @@ class Model:
         self.n_params = sum(t.numel() for t in tensors.values())
         self.embedding.bind(tensors)
         self.head.bind(tensors, self.embedding)      # a tied head takes the embedding's table
-        self.final_norm.bind(tensors[spec.final_norm["name"]])
+        bind_norm(self.final_norm, spec.final_norm, tensors, spec.final_norm["name"])
         for layer, block in zip(spec.layers, self.blocks):
             n = len(layer.prefix)
             block.bind({k[n:]: v for k, v in tensors.items() if k.startswith(layer.prefix)})

@@ -20,7 +20,7 @@ __all__ = ["KernelError", "KernelBuildError", "embed_rows", "rmsnorm", "qknorm_r
            "attention", "sample_rows", "sample_filtered", "recent_set", "seed_slots", "embed_pair_norm",
            "canon_conv", "norm_canon_single", "latent_keep", "head_product", "head_gate", "gated_add", "xielu",
            "proj_norm_rope_cache", "rotate_heads", "short_conv", "state_scan", "head_norm_gate", "gate_mul",
-           "norm_add", "norm_shift", "scan_gates_step", "scan_gates_max", "state_readout", "pool_update", "moe_route", "moe_plan", "moe_gemm", "moe_gemv", "moe_gather", "moe_gemm_tc", "moe_combine", "moe_combine_norm_add", "moe_tile_rows"]
+           "norm_add", "norm_shift", "scan_gates_step", "scan_gates_max", "state_readout", "pool_update", "moe_route", "moe_plan", "moe_gemm", "moe_gemv", "moe_gather", "moe_gemm_tc", "moe_combine", "moe_combine_norm_add", "moe_tile_rows", "tanh_norm", "scaled_join", "relu2", "selective_scan", "diff_combine"]
 
 F32, BF16 = 0, 1
 EPI_STORE_F32, EPI_STORE_BF16, EPI_ACCUM_F32 = 0, 1, 2
@@ -148,6 +148,44 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
     f = _fn("elementwise.cu", "g2b_rmsnorm",
             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p])
     _call(f, _ptr(x), _ptr(w), _ptr(rows), n_rows, H, eps, _ptr(out), _code(out.dtype), _stream())
+
+
+def tanh_norm(x: torch.Tensor, alpha: torch.Tensor, w: torch.Tensor, b: torch.Tensor, out: torch.Tensor,
+              rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = tanh(alpha * x[row_r]) * w + b: a norm that takes no statistics of the row.  x, w, b
+    float32, ``alpha`` float32 with one element (read on the device); ``rows`` (int32) gathers rows."""
+    _need(x, torch.float32, "x")
+    for t, what in ((alpha, "alpha"), (w, "norm weight"), (b, "norm bias")):
+        _need(t, torch.float32, what)
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+    if not out.is_contiguous():
+        raise KernelError("tanh_norm: out must be contiguous")
+    n_rows, H = out.shape
+    f = _fn("elementwise.cu", "g2b_tanh_norm",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p])
+    _call(f, _ptr(x), _ptr(alpha), _ptr(w), _ptr(b), _ptr(rows), n_rows, H, _ptr(out), _code(out.dtype), _stream())
+
+
+def scaled_join(x32, y1, s1, y2=None, s2=None) -> None:
+    """x += y1 * s1 (+ y2 * s2): sublayer results [T, H] join the stream, each times one learned number
+    per channel ([H]); everything float32."""
+    for t, what in ((x32, "stream"), (y1, "result"), (s1, "scale")):
+        _need(t, torch.float32, what)
+    if y2 is not None:
+        _need(y2, torch.float32, "second result")
+        _need(s2, torch.float32, "second scale")
+    f = _fn("elementwise.cu", "g2b_scaled_join", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _call(f, _ptr(x32), _ptr(y1), _ptr(s1), _ptr(y2), _ptr(s2) if y2 is not None else None, x32.shape[0], x32.shape[1],
+          _stream())
+
+
+def relu2(z, out) -> None:
+    """out = max(z, 0)^2; z [T, F] a view with any row stride, out [T, F] contiguous, one dtype."""
+    if z.stride(1) != 1 or out.dtype != z.dtype or not out.is_contiguous():
+        raise KernelError("relu2: dense rows of one dtype")
+    f = _fn("elementwise.cu", "g2b_relu2", [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _call(f, _ptr(z), z.stride(0), _code(z.dtype), z.shape[0], z.shape[1], _ptr(out), _stream())
 
 
 def rope_table(tok_pos: torch.Tensor, inv_freq: torch.Tensor, table: torch.Tensor, mult: float = 1.0) -> None:
@@ -461,7 +499,7 @@ def attention_notices(what: str, head_dim: int, page_size: int, compute_dtype: t
 # ---------------------------------------------------------------------------
 def attn_generic(q, out, cache_pages, tok_pos, tok_seq, page_table, n_heads, n_kv_heads,
                  head_dim, page_size, window, scale, sink=None, planes: int = 2, gate=None, chunk: int = 0,
-                 pooled=None, pool: int = 0) -> None:
+                 pooled=None, pool: int = 0, softcap: float = 0.0, keep_first: int = 0, v_heads: int = 0) -> None:
     """Causal attention of every token of the step over its sequence's cache pages,
     32-bit arithmetic; q [T, n_heads*head_dim] (rows may lie further apart: columns of a wider
     buffer), out [T, n_heads*head_dim] contiguous.  ``sink`` (float32 [n_heads]): one more
@@ -471,11 +509,13 @@ def attn_generic(q, out, cache_pages, tok_pos, tok_seq, page_table, n_heads, n_k
     a token sees the keys of its own chunk of that many positions only (counted from position 0).
     ``pool`` > 0 with ``pooled`` [pages, 2, kv heads, rows, head_dim] (and a window): in front of the
     window a token also sees the mean key and value of every block of ``pool`` positions that lies
-    wholly before the window, in the same softmax."""
+    wholly before the window, in the same softmax.  ``softcap`` > 0: scores become softcap * tanh(score /
+    softcap).  ``keep_first`` > 0 (with a window): the first that many positions stay visible behind the
+    window.  ``v_heads`` (a divisor of the kv heads): key head g reads the values of head g mod v_heads."""
     f = _fn("attn_generic.cu", "g2b_attn_generic",
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
              c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
-             c_int, c_int, c_void_p])
+             c_int, c_int, c_float, c_int, c_int, c_void_p])
     if pool and (pooled is None or pooled.dtype != q.dtype):
         raise KernelError("attention: pooled blocks need their store, of q's dtype")
     if q.dtype != cache_pages.dtype or out.dtype != q.dtype:
@@ -488,14 +528,16 @@ def attn_generic(q, out, cache_pages, tok_pos, tok_seq, page_table, n_heads, n_k
           _ptr(page_table), page_table.shape[1], q.shape[0], n_heads, n_kv_heads, head_dim,
           page_size, window, scale, _ptr(sink), planes, q.stride(0), _ptr(gate),
           gate.stride(0) if gate is not None else 0, int(chunk), _ptr(pooled) if pool else None, int(pool),
-          pooled.shape[3] if pool else 0, _stream())
+          pooled.shape[3] if pool else 0, float(softcap), int(keep_first), int(v_heads), _stream())
 
 
 def attention(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
-              scale, sink=None, planes: int = 2, gate=None, chunk: int = 0, pooled=None, pool: int = 0) -> None:
+              scale, sink=None, planes: int = 2, gate=None, chunk: int = 0, pooled=None, pool: int = 0,
+              softcap: float = 0.0, keep_first: int = 0, v_heads: int = 0) -> None:
     """Attention of a step: the tensor-core kernels when they take the case, else the
     32-bit kernel.  ``q`` and ``gate`` may be column ranges of a wider buffer.  ``pool``, ``pooled``:
-    mean keys and values of whole blocks in front of the window (``attn_generic``)."""
+    mean keys and values of whole blocks in front of the window (``attn_generic``).  ``softcap``,
+    ``keep_first``, ``v_heads``: as ``attn_generic``."""
     if pool:
         if q.dtype == torch.bfloat16 and (_bf16 or _bf16_mod()).attention_pooled_bf16(
                 q, out, cache_pages, pooled, ctx, n_heads, n_kv_heads, head_dim, page_size, window, pool, scale):
@@ -505,10 +547,12 @@ def attention(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size
         return
     if q.dtype == torch.bfloat16:
         if (_bf16 or _bf16_mod()).attention_bf16(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim,
-                                       page_size, window, scale, sink, planes, gate, chunk):
+                                       page_size, window, scale, sink, planes, gate, chunk,
+                                       softcap=softcap, keep_first=keep_first, v_heads=v_heads):
             return
     attn_generic(q, out, cache_pages, ctx.tok_pos, ctx.tok_seq, ctx.page_table, n_heads,
-                 n_kv_heads, head_dim, page_size, window, scale, sink, planes, gate, chunk)
+                 n_kv_heads, head_dim, page_size, window, scale, sink, planes, gate, chunk,
+                 softcap=softcap, keep_first=keep_first, v_heads=v_heads)
 
 
 def normed_product(x32, eps, w, out, gate_block=None) -> bool:
@@ -617,17 +661,23 @@ def _dense_rows(t: torch.Tensor, what: str) -> int:
 
 
 def proj_norm_rope_cache(qkv, bias, n_heads, n_kv_heads, qk_dim, v_dim, q_w, k_w, eps, rope, rotary_dim,
-                         interleaved, ctx, cache_pages, page_size, q_out, v_norm_eps: float = 0.0) -> None:
+                         interleaved, ctx, cache_pages, page_size, q_out, v_norm_eps: float = 0.0,
+                         norm_per_head: bool = False, unit_eps: float = 0.0, n_v_heads: Optional[int] = None) -> None:
     """q, k, v side by side in ``qkv`` [T, nh*D + nkv*D + nkv*V] (+ ``bias``, float32); RMS norm over
     ALL of q and over all of k (weights ``q_w`` [nh*D], ``k_w`` [nkv*D]; None: no norm); rotation by
     the step's ``rope`` table, pairs (i, i + r/2) or, ``interleaved``, (2i, 2i + 1); q to ``q_out``
     [T, nh*hd] and k, v into the pages, heads zero-filled to hd = max(D, V).  ``v_norm_eps`` > 0: every
-    value head is divided by its root mean square (that eps inside the root) before it is stored."""
+    value head is divided by its root mean square (that eps inside the root) before it is stored.
+    ``norm_per_head``: the norm runs over every head of q and k by itself, the weights ``q_w``, ``k_w`` [D]
+    shared by the heads.  ``unit_eps`` > 0: after the rotation every head of q and k is divided by its
+    root mean square (that eps inside the root, no weight).  ``n_v_heads``: fewer value heads than key
+    heads (``qkv`` then ends with that many; the other value panels of the pages stay unused).
+    ``n_kv_heads`` 0 (``cache_pages`` None): q alone, for a layer that reads another layer's pages."""
     f = _fn("seq_mix.cu", "g2b_proj_norm_rope_cache",
             [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
              c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_float,
-             c_void_p])
-    if q_out.dtype != qkv.dtype or cache_pages.dtype != qkv.dtype or not q_out.is_contiguous():
+             c_int, c_float, c_int, c_void_p])
+    if q_out.dtype != qkv.dtype or (cache_pages is not None and cache_pages.dtype != qkv.dtype) or not q_out.is_contiguous():
         raise KernelError("proj_norm_rope_cache: q_out and the cache must have the input's dtype")
     for t in (bias, q_w, k_w):
         if t is not None:
@@ -635,7 +685,8 @@ def proj_norm_rope_cache(qkv, bias, n_heads, n_kv_heads, qk_dim, v_dim, q_w, k_w
     _call(f, _ptr(qkv), _code(qkv.dtype), _dense_rows(qkv, "qkv"), qkv.shape[0], _ptr(bias), n_heads, n_kv_heads,
           qk_dim, v_dim, _ptr(q_w), _ptr(k_w), eps, _ptr(rope), rotary_dim, 1 if interleaved else 0,
           _ptr(ctx.tok_pos), _ptr(ctx.tok_seq), _ptr(ctx.page_table), ctx.page_table.shape[1],
-          _ptr(cache_pages), page_size, _ptr(q_out), float(v_norm_eps), _stream())
+          _ptr(cache_pages), page_size, _ptr(q_out), float(v_norm_eps), 1 if norm_per_head else 0, float(unit_eps),
+          n_kv_heads if n_v_heads is None else int(n_v_heads), _stream())
 
 
 def rotate_heads(x, heads, head_dim, rope, rotary_dim, interleaved, scale: float = 1.0) -> None:
@@ -830,6 +881,41 @@ def norm_add(x32, y32, w, eps, cast_out=None) -> None:
           _code(cast_out.dtype) if cast_out is not None else F32, _stream())
 
 
+def selective_scan(x, dt32, dt_bias, bc, a, skip, z, state, ctx, out, out_scale: float = 1.0) -> None:
+    """A state-space recurrence with a decay per state entry, over the step's tokens in order:
+    dt = softplus(dt32 + dt_bias); S[c, n] = exp(dt_c a[c, n]) S[c, n] + dt_c x_c B_n; y_c = sum_n S[c, n] C_n;
+    out = (y + skip * x) * silu(z) * out_scale.  x, z [T, inner] and ``bc`` [T, 2N] (B, then C) in the
+    compute type, rows may lie apart; ``dt32`` float32 [T, inner]; ``a`` float32 [inner, N] (negative);
+    ``state`` float32 [slots, inner, N] is read and left up to date."""
+    T, inner = x.shape
+    N = a.shape[1]
+    for t, what in ((dt32, "step sizes"), (dt_bias, "dt bias"), (a, "decay rates"), (skip, "skip"), (state, "state")):
+        _need(t, torch.float32, what)
+    if z.dtype != x.dtype or bc.dtype != x.dtype or out.dtype != x.dtype:
+        raise KernelError("selective_scan: x, z, B/C and out must have one dtype")
+    if tuple(state.shape[1:]) != (inner, N) or bc.shape[1] != 2 * N or tuple(a.shape) != (inner, N):
+        raise KernelError(f"selective_scan: state {tuple(state.shape)}, B/C {tuple(bc.shape)} or rates {tuple(a.shape)} "
+                          f"do not fit {inner} channels of {N} entries")
+    f = _fn("seq_mix.cu", "g2b_selective_scan",
+            [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p])
+    _call(f, _ptr(x), _code(x.dtype), _dense_rows(x, "x"), _ptr(dt32), _dense_rows(dt32, "dt"), _ptr(dt_bias), _ptr(bc),
+          _dense_rows(bc, "B/C"), _ptr(a), _ptr(skip), _ptr(z), _dense_rows(z, "z"), _ptr(state), _ptr(ctx.seq_slots),
+          _ptr(ctx.seq_meta), T, ctx.n_seqs, inner, N, float(out_scale), _ptr(out), _dense_rows(out, "out"), _stream())
+
+
+def diff_combine(a, heads: int, head_dim: int, v_dim: int, lam: float, eps: float, post: float, out) -> None:
+    """Two attention maps per head, ``a`` [T, 2 * heads * head_dim] (all heads of the first map, then of
+    the second; ``v_dim`` entries of a head in use): out[t, h] = (a1 - lam * a2) / sqrt(mean(.^2) + eps) *
+    post, [T, heads * v_dim]."""
+    if not a.is_contiguous() or not out.is_contiguous() or out.dtype != a.dtype:
+        raise KernelError("diff_combine: contiguous tensors of one dtype")
+    f = _fn("seq_mix.cu", "g2b_diff_combine",
+            [c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p, c_void_p])
+    _call(f, _ptr(a), _code(a.dtype), a.shape[0], heads, head_dim, v_dim, float(lam), float(eps), float(post), _ptr(out),
+          _stream())
+
+
 # ---------------------------------------------------------------------------
 # moe.cu: a routed feed-forward
 # ---------------------------------------------------------------------------
@@ -838,17 +924,22 @@ def moe_tile_rows() -> int:
     return int(lib.g2b_moe_tile_rows())
 
 
-def moe_route(z32, correction, top: int, renormalise: bool, idx, weight, scale: float = 1.0) -> None:
-    """softmax over all experts of ``z32`` [T, N]; the ``top`` largest of score + correction chosen
-    (``idx`` int32 [T, top]); ``weight`` float32 [T, top] their scores (divided by their sum when
-    ``renormalise``), times ``scale``."""
+def moe_route(z32, correction, top: int, renormalise: bool, idx, weight, scale: float = 1.0, score: str = "softmax",
+              groups: int = 1, keep: int = 1) -> None:
+    """softmax over all experts of ``z32`` [T, N] (``score`` "sigmoid": every logit's sigmoid by itself);
+    the ``top`` largest of score + correction chosen (``idx`` int32 [T, top]); ``weight`` float32 [T, top]
+    their scores (divided by their sum + 1e-20 when ``renormalise``), times ``scale``.  ``groups`` > 1: the
+    experts are that many equal groups of neighbours, a group counts as the sum of its two best scores,
+    and only experts of the ``keep`` best groups can be chosen."""
+    if score not in ("softmax", "sigmoid"):
+        raise KernelError(f"moe_route: scores are 'softmax' or 'sigmoid', not {score!r}")
     _need(z32, torch.float32, "router logits")
     _need(idx, torch.int32, "idx")
     _need(weight, torch.float32, "weight")
     f = _fn("moe.cu", "g2b_moe_route", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
-                                        c_void_p])
+                                        c_int, c_int, c_int, c_void_p])
     _call(f, _ptr(z32), _ptr(correction), z32.shape[0], z32.shape[1], top, 1 if renormalise else 0, _ptr(idx),
-          _ptr(weight), float(scale), _stream())
+          _ptr(weight), float(scale), 1 if score == "sigmoid" else 0, int(groups), int(keep), _stream())
 
 
 def moe_plan(idx, n_real: int, max_tiles: int, plan, row_pair, pair_row) -> None:

@@ -305,8 +305,11 @@ def gate_up_bf16(h: torch.Tensor, w_gate_up: torch.Tensor, mid: torch.Tensor, bl
 
 
 def attention_bf16(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
-                   scale, sink=None, planes: int = 2, gate=None, chunk: int = 0) -> bool:
+                   scale, sink=None, planes: int = 2, gate=None, chunk: int = 0, softcap: float = 0.0,
+                   keep_first: int = 0, v_heads: int = 0) -> bool:
     """``chunk`` > 0 (keys of the token's own chunk only) reaches the kernels as a negative window."""
+    if softcap or keep_first or (v_heads and v_heads != n_kv_heads):
+        return False              # capped scores, kept first tokens and shared value heads: the 32-bit kernel
     if chunk:
         if window:
             return False

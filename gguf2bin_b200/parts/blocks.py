@@ -5,7 +5,9 @@ OUTPUT and the sublayers read the stream itself.
 ``gated_prenorm``: the same with each sublayer's result scaled by a learned gate, an optional
 short convolution over time in front of the mixer, and an optional feed-forward.
 ``parallel_shift``: h = norm(x); x += mixer(shift(h)) + feed_forward(h): one norm, both sublayers read
-it, and the mixer's copy is mixed with the token before, channel by channel."""
+it, and the mixer's copy is mixed with the token before, channel by channel.
+``parallel_scaled``: h = norm(x); x += s1 * mixer(h) + s2 * feed_forward(h): one norm of any registered kind,
+both sublayers read it, and each result is multiplied by a learned number per channel before the sum."""
 from __future__ import annotations
 
 import torch
@@ -15,7 +17,7 @@ from ..cache.storage import StateNeed
 from ..config.specs import ConfigError, LayerSpec
 from ..weights.loader import Expected
 from .feed_forward import RoutedExperts
-from .norms import RMSNorm
+from .norms import RMSNorm, bind_norm
 from .registry import (feed_forward_class, mixer_class, norm_class, register_block)
 
 
@@ -445,7 +447,88 @@ class ParallelShiftBlock:
             self.feed_forward.forward(h, ctx, x32)
 
 
+class ParallelScaledBlock:
+    """``parallel_scaled``: with h = norm(x), x <- x + (s1 * mixer(h) + s2 * feed_forward(h)); s1 and s2 are
+    stored vectors of the model's width (names ``mixer_scale``, ``ffn_scale``), applied to each sublayer's
+    whole result in 32-bit before the two are added and join the stream.  A layer may have no feed-forward.
+    Any norm, mixer and feed-forward of the library fit: a sublayer stores into a 32-bit buffer of its own
+    where it can (``forward_store``, ``forward_into``) and adds into a cleared one where it cannot."""
+
+    def __init__(self, layer: LayerSpec, hidden_size: int, dtype: torch.dtype, device):
+        self.names = dict(layer.block["names"])
+        self.hidden, self.dtype = int(hidden_size), dtype
+        self.norm_spec = layer.norm
+        self.norm = norm_class(layer.norm)(layer.norm, hidden_size, dtype, device)
+        self.mixer = mixer_class(layer.mixer)(layer.mixer, hidden_size, dtype, device)
+        self.feed_forward = None
+        if layer.feed_forward is not None:
+            self.feed_forward = feed_forward_class(layer.feed_forward)(layer.feed_forward, hidden_size, dtype, device)
+        self.mixer_scale = self.ffn_scale = None
+
+    @classmethod
+    def expected(cls, layer: LayerSpec, hidden_size: int) -> dict:
+        names = dict(layer.block["names"])
+        out = {names["mixer_scale"]: Expected((int(hidden_size),), init="scale")}
+        out.update(norm_class(layer.norm).expected(layer.norm, hidden_size, names["norm"]))
+        out.update(mixer_class(layer.mixer).expected(layer.mixer, hidden_size))
+        if layer.feed_forward is not None:
+            out[names["ffn_scale"]] = Expected((int(hidden_size),), init="scale")
+            out.update(feed_forward_class(layer.feed_forward).expected(layer.feed_forward, hidden_size))
+        else:        # a checkpoint may carry the second vector all the same; it is unused
+            out[names["ffn_scale"]] = Expected((int(hidden_size),), init="scale", optional=True)
+        return out
+
+    def bind(self, tensors: dict) -> None:
+        bind_norm(self.norm, self.norm_spec, tensors, self.names["norm"])
+        self.mixer_scale = tensors[self.names["mixer_scale"]].to(torch.float32).contiguous()
+        self.mixer.bind(tensors)
+        if self.feed_forward is not None:
+            self.ffn_scale = tensors[self.names["ffn_scale"]].to(torch.float32).contiguous()
+            self.feed_forward.bind(tensors)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def parts(self) -> tuple:
+        return tuple(p for p in (self.norm, self.mixer, self.feed_forward) if p is not None)
+
+    def weights(self):
+        for part in self.parts():
+            yield from getattr(part, "weights", tuple)()
+        for t in (self.mixer_scale, self.ffn_scale):
+            if t is not None:
+                yield t
+
+    def notices(self) -> list:
+        return [line for part in self.parts() for line in getattr(part, "notices", list)()]
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(part, "graph_safe", False) for part in self.parts())
+
+    def forward(self, x32: torch.Tensor, ctx, cache_view) -> None:
+        T, H, ws = x32.shape[0], self.hidden, ctx.workspace
+        h = ws.buffer("pscaled.normed", (T, H), self.dtype)
+        self.norm.forward(x32, h)
+        y1 = ws.buffer("pscaled.mixer", (T, H), torch.float32)
+        if hasattr(self.mixer, "forward_store"):
+            self.mixer.forward_store(h, ctx, cache_view, y1)
+        else:
+            y1.zero_()
+            self.mixer.forward(h, ctx, cache_view, y1)
+        y2, ff = None, self.feed_forward
+        if ff is not None:
+            y2 = ws.buffer("pscaled.ffn", (T, H), torch.float32)
+            if hasattr(ff, "forward_into"):
+                ff.forward_into(h, ctx, y2)
+            else:
+                y2.zero_()
+                ff.forward(h, ctx, y2)
+        kernels.scaled_join(x32, y1, self.mixer_scale, y2, self.ffn_scale)
+
+
 register_block("prenorm", PreNormBlock)
+register_block("parallel_scaled", ParallelScaledBlock)
 register_block("parallel_shift", ParallelShiftBlock)
 register_block("gated_prenorm", GatedPreNormBlock)
 register_block("branch_norm", BranchNormBlock)

@@ -91,7 +91,8 @@ class SwiGLU:
 class ActMLP:
     """``act_mlp``: down( act(up x) ), two matrices and an elementwise activation.  Activations:
     ``xielu``, a z^2 + z/2 above zero and (1/2 + b)(exp(z) - 1 - z) + z/2 below, with a and b the
-    softplus of two learned numbers (one tensor of two), computed in 32-bit.
+    softplus of two learned numbers (one tensor of two), computed in 32-bit; ``relu2``, max(z, 0)^2,
+    which has no tensor of its own.
 
     A block may hand it one more matrix that reads the same input (``take_along``): its rows go
     under the up matrix, one product computes both, and the step leaves that matrix's output in
@@ -101,8 +102,8 @@ class ActMLP:
     def __init__(self, spec: PartSpec, hidden_size: int, dtype: torch.dtype, device):
         self.inter, self.hidden = int(spec["intermediate_size"]), int(hidden_size)
         self.activation = spec.get("activation") or "xielu"
-        if self.activation != "xielu":
-            raise ConfigError(f"act_mlp: activation {self.activation!r} is not known (known: 'xielu')")
+        if self.activation not in ("xielu", "relu2"):
+            raise ConfigError(f"act_mlp: activation {self.activation!r} is not known (known: 'xielu', 'relu2')")
         self.dtype = dtype
         self.names = dict(spec["names"])
         self.w_up = self.w_down = self.act = None
@@ -112,13 +113,16 @@ class ActMLP:
     @classmethod
     def expected(cls, spec: PartSpec, hidden_size: int) -> dict:
         n, inter = dict(spec["names"]), spec["intermediate_size"]
-        return {n["up"]: Expected((inter, hidden_size)), n["down"]: Expected((hidden_size, inter)),
-                n["act"]: Expected((2,))}
+        out = {n["up"]: Expected((inter, hidden_size)), n["down"]: Expected((hidden_size, inter))}
+        if (spec.get("activation") or "xielu") == "xielu":
+            out[n["act"]] = Expected((2,))
+        return out
 
     def bind(self, tensors: dict) -> None:
         self.w_up = tensors[self.names["up"]].contiguous()
         self.w_down = tensors[self.names["down"]].contiguous()
-        self.act = tensors[self.names["act"]].to(torch.float32).contiguous()
+        if self.activation == "xielu":
+            self.act = tensors[self.names["act"]].to(torch.float32).contiguous()
 
     def take_along(self, w_side: torch.Tensor) -> bool:
         """Puts ``w_side`` [n, hidden] under the up matrix; True when taken (equal dtypes, and an
@@ -134,7 +138,7 @@ class ActMLP:
         return True
 
     def weights(self):
-        return (self.w_up, self.w_down, self.act)
+        return tuple(t for t in (self.w_up, self.w_down, self.act) if t is not None)
 
     def notices(self) -> list:
         return (kernels.product_notices("feed-forward up", self.w_up, self.dtype)
@@ -154,7 +158,10 @@ class ActMLP:
         kernels.linear(h, self.w_up, up)
         self.side_out = up[:, self.inter:self.inter + self.n_side] if self.n_side else None
         mid = ws.buffer("mlp.mid", (T, self.inter), self.dtype)
-        kernels.xielu(up[:, :self.inter], self.act, mid)
+        if self.activation == "relu2":
+            kernels.relu2(up[:, :self.inter], mid)
+        else:
+            kernels.xielu(up[:, :self.inter], self.act, mid)
         kernels.linear(mid, self.w_down, out32, accumulate=accumulate)
 
 
@@ -166,7 +173,10 @@ class RoutedExperts:
     its score as it is (``renormalise``: divided by the chosen scores' sum).  The last ``n_identity``
     router outputs stand for experts without matrices whose output is their input.  The result is
     the weighted sum of the chosen experts' outputs, added in the order of the choice.  ``scale``: every
-    weight times that constant.  ``shared``: the spec of one more feed-forward (any registered kind)
+    weight times that constant.  ``score`` = "sigmoid": the scores are the logits' sigmoids, each by itself,
+    instead of a softmax.  ``groups`` with ``groups_kept``: the experts form that many equal groups of
+    neighbours, a group counts as the sum of its two largest scores, and only experts of the best
+    ``groups_kept`` groups can be chosen.  ``shared``: the spec of one more feed-forward (any registered kind)
     that runs for every token and is added.
 
     A step groups its (token, choice) pairs by expert on the device (``moe_plan``) and runs one
@@ -188,6 +198,14 @@ class RoutedExperts:
         self.w_router = self.correction = self.w_gate_up = self.w_down = None
         self.blocked = False
         self.scale = float(spec.get("scale") if spec.get("scale") is not None else 1.0)
+        self.score = spec.get("score") or "softmax"
+        self.groups = int(spec.get("groups") or 1)
+        self.groups_kept = int(spec.get("groups_kept") or self.groups)
+        n_all = self.E + self.I
+        if self.score not in ("softmax", "sigmoid") or self.groups < 1 or n_all % self.groups \
+                or not (1 <= self.groups_kept <= self.groups) or self.top > self.groups_kept * (n_all // self.groups):
+            raise ConfigError(f"routed_experts: scores 'softmax' or 'sigmoid'; {n_all} experts in {self.groups} equal "
+                              f"groups of which {self.groups_kept} are kept must hold {self.top} choices")
         shared = spec.get("shared")
         self.shared = feed_forward_class(shared)(shared, hidden_size, dtype, device) if shared is not None else None
 
@@ -253,9 +271,9 @@ class RoutedExperts:
         """Stores the result.  ``x_self32``: the input in 32-bit, for the experts whose output is their
         input (default: ``h`` widened)."""
         rows32, pair_row, weight = self._experts(h, ctx)
-        if x_self32 is None:
+        if x_self32 is None and self.I:
             x_self32 = h if h.dtype == torch.float32 else h.float()
-        kernels.moe_combine(rows32, pair_row, weight, x_self32, self.top, out32)
+        kernels.moe_combine(rows32, pair_row, weight, x_self32 if self.I else rows32, self.top, out32)
         if self.shared is not None:
             self.shared.forward(h, ctx, out32)
 
@@ -275,7 +293,8 @@ class RoutedExperts:
         kernels.linear(h, self.w_router, z)
         idx = ws.buffer("moe.idx", (T, top), torch.int32)
         weight = ws.buffer("moe.weight", (T, top), torch.float32)
-        kernels.moe_route(z, self.correction, top, self.renormalise, idx, weight, self.scale)
+        kernels.moe_route(z, self.correction, top, self.renormalise, idx, weight, self.scale, self.score, self.groups,
+                          self.groups_kept)
         n_pairs = T * top
         tile = kernels.moe_tile_rows()
         max_tiles = -(-n_pairs // tile) + E               # every expert's last tile may be part full

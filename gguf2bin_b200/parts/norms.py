@@ -2,7 +2,11 @@
 the weight a plain multiplier (src/l3_math.c:21-51 of AnonymoDGH/gguf2bin).  With ``offset`` the
 stored tensor is the weight's distance from that number (a checkpoint that keeps its norm
 weights around zero has ``offset`` 1): the multiplier is ``offset + stored``, added once, in
-32-bit, when the weights are bound."""
+32-bit, when the weights are bound.
+``tanh_norm``: o_j = tanh(alpha * x_j) * w_j + b_j with one learned number alpha: no mean, no variance,
+nothing summed over the row.  Its three tensors are ``<name>``, ``<name><bias_suffix>`` and
+``<name><alpha_suffix>`` (suffixes ".b" and ".alpha" unless the spec says otherwise); a block binds it
+through ``bind_norm``, which hands a norm with more than one tensor all of them."""
 from __future__ import annotations
 
 import torch
@@ -52,4 +56,43 @@ class RMSNorm:
         kernels.rmsnorm(x32, self.weight, self.eps, out, rows)
 
 
+class TanhNorm:
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, width: int, dtype: torch.dtype, device):
+        self.width = int(width)
+        self.weight = self.bias = self.alpha = None
+
+    @staticmethod
+    def _names(spec: PartSpec, name: str):
+        return name, name + (spec.get("bias_suffix") or ".b"), name + (spec.get("alpha_suffix") or ".alpha")
+
+    @classmethod
+    def expected(cls, spec: PartSpec, width: int, name: str) -> dict:
+        w, b, a = cls._names(spec, name)
+        return {w: Expected((int(width),), init="scale"), b: Expected((int(width),)), a: Expected((), init="scale")}
+
+    def bind_named(self, spec: PartSpec, tensors: dict, name: str) -> None:
+        w, b, a = self._names(spec, name)
+        self.weight = tensors[w].to(torch.float32).contiguous()
+        self.bias = tensors[b].to(torch.float32).contiguous()
+        self.alpha = tensors[a].to(torch.float32).reshape(1).contiguous()      # stays on the device: read by the kernel
+
+    def weights(self):
+        return tuple(t for t in (self.weight, self.bias, self.alpha) if t is not None)
+
+    def forward(self, x32: torch.Tensor, out: torch.Tensor, rows=None) -> None:
+        kernels.tanh_norm(x32, self.alpha, self.weight, self.bias, out, rows)
+
+
+def bind_norm(norm, spec: PartSpec, tensors: dict, name: str) -> None:
+    """Hands a norm its tensors: the one called ``name``, or, for a norm that has several
+    (``bind_named``), all that it listed under that name."""
+    if hasattr(norm, "bind_named"):
+        norm.bind_named(spec, tensors, name)
+    else:
+        norm.bind(tensors[name])
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("tanh_norm", TanhNorm)

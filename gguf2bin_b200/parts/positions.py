@@ -13,7 +13,8 @@ longer than the ``original`` length: with pair(t) = r ln(original / (2 pi t)) / 
 index that makes t turns over ``original`` positions, lo = max(floor(pair(fast)), 0),
 hi = min(ceil(pair(slow)), r - 1) and ramp_j = clamp((j - lo) / max(hi - lo, 0.001), 0, 1), pair j
 turns at f_j (1 - ramp_j) + (f_j / factor) ramp_j, and cos and sin are both multiplied by
-0.1 ln(factor) + 1 (``mult``; the step's table carries it).
+0.1 ln(factor) + 1 (``mult``; the step's table carries it).  With ``interleaved`` the same frequencies
+turn neighbouring pairs (2j, 2j + 1).
 ``none``: nothing is applied.
 """
 from __future__ import annotations
@@ -97,16 +98,20 @@ class RopeStretched(RopeNeox):
         self.inv_freq = _INV_FREQ[key]
         import math
         self.mult = 0.1 * math.log(factor) + 1.0
+        self.interleaved = bool(spec.get("interleaved") or False)
 
     def fused_rotation(self):
-        return None if self.mult != 1.0 else (self.inv_freq, self.rotary_dim)     # the fused kernel's table has no factor
+        if self.mult != 1.0 or self.interleaved:       # the fused kernel's table has no factor, its pairs are (j, j + r/2)
+            return None
+        return self.inv_freq, self.rotary_dim
 
     def apply(self, q, k, ctx) -> None:
         from .. import kernels
         rope = ctx.rope_table(self.inv_freq, self.mult)
         for a in (q, k):
             if a is not None and a.numel():
-                kernels.rotate_heads(a, a.shape[1] // self.head_dim, self.head_dim, rope, self.rotary_dim, False)
+                kernels.rotate_heads(a, a.shape[1] // self.head_dim, self.head_dim, rope, self.rotary_dim,
+                                     self.interleaved)
 
 
 class RopeInterleaved(RopeNeox):

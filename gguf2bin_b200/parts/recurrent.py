@@ -29,6 +29,14 @@ S = exp(f + m - m') S + exp(i - m') k v^T, n likewise with k alone, o = S^T q / 
 each head's o divided by its root mean square, times a weight over all heads, times sigmoid(W_g h);
 output product.  n rides in the scan as one more column of S whose value is always 1.
 
+``selective_ssm``: a state-space mixer with a decay per channel AND state entry (the selective scan).
+W_in h = [x: inner | z: inner]; x through a causal convolution per channel (``conv_taps`` taps with a bias,
+the last the current token's) and SiLU; W_x x = [dt: dt_rank | B: state_dim | C: state_dim];
+dt = softplus(W_dt dt + dt_bias), one per channel; A = -exp(A_log) [inner, state_dim]; per channel c and
+entry n: S[c, n] = exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n, y_c = sum_n S[c, n] C_n + D_c x_c; y silu(z);
+output product.  The state [inner, state_dim] is 32-bit and starts at zero; the convolution's last
+inputs are a ring by position.  Step sizes, decays and the recurrence are 32-bit.
+
 ``parallel``: several mixers that read the same input; the result is the sum of theirs, each times
 its ``out_scale``.  A branch is any registered mixer that takes ``out_scale``.
 
@@ -308,6 +316,79 @@ class SSDMixer:
         kernels.linear(og, self.w_o, residual32, accumulate=accumulate)
 
 
+class SelectiveSSM:
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, hidden_size: int, dtype: torch.dtype, device):
+        self.inner, self.N, self.R = int(spec["inner"]), int(spec["state_dim"]), int(spec["dt_rank"])
+        self.taps = int(spec["conv_taps"])
+        self.hidden, self.dtype, self.device = int(hidden_size), dtype, device
+        if min(self.inner, self.R) <= 0 or not (1 <= self.N <= 256) or not (1 <= self.taps <= 16):
+            raise ConfigError("selective_ssm: inner and dt_rank positive, state_dim in 1..256, conv_taps in 1..16")
+        self.out_scale = float(spec.get("out_scale") if spec.get("out_scale") is not None else 1.0)
+        self.names = dict(spec["names"])
+        self.w_in = self.w_conv = self.b_conv = self.w_x = self.w_dt = self.dt_bias = self.a = self.skip = self.w_o = None
+
+    @classmethod
+    def expected(cls, spec: PartSpec, hidden_size: int) -> dict:
+        n = dict(spec["names"])
+        inner, N, R, taps = (int(spec[k]) for k in ("inner", "state_dim", "dt_rank", "conv_taps"))
+        return {n["in"]: Expected((2 * inner, hidden_size)), n["conv"]: Expected((inner, taps)),
+                n["conv_bias"]: Expected((inner,)), n["x"]: Expected((R + 2 * N, inner)), n["dt"]: Expected((inner, R)),
+                n["dt_bias"]: Expected((inner,)), n["a_log"]: Expected((inner, N)), n["skip"]: Expected((inner,)),
+                n["o"]: Expected((hidden_size, inner))}
+
+    def bind(self, tensors: dict) -> None:
+        n = self.names
+        self.w_in = _padded_rows([tensors[n["in"]]])                  # x | z
+        self.w_conv = tensors[n["conv"]].to(torch.float32).t().contiguous()          # [taps, channels]
+        self.b_conv = tensors[n["conv_bias"]].to(torch.float32).contiguous()
+        self.w_x = _padded_rows([tensors[n["x"]]])                    # dt | B | C (| zeros)
+        self.w_dt = tensors[n["dt"]].contiguous()
+        self.dt_bias = tensors[n["dt_bias"]].to(torch.float32).contiguous()
+        self.a = (-torch.exp(tensors[n["a_log"]].to(torch.float32))).contiguous()    # the decay rates, 32-bit
+        self.skip = tensors[n["skip"]].to(torch.float32).contiguous()
+        self.w_o = tensors[n["o"]].contiguous()
+
+    def weights(self):
+        return (self.w_in, self.w_conv, self.b_conv, self.w_x, self.w_dt, self.dt_bias, self.a, self.skip, self.w_o)
+
+    def notices(self) -> list:
+        return (kernels.product_notices("state-space input", self.w_in, self.dtype)
+                + kernels.product_notices("state-space step size", self.w_dt, self.dtype)
+                + kernels.product_notices("state-space output", self.w_o, self.dtype))
+
+    def cache_need(self):
+        need = {"state": StateNeed((self.inner, self.N), torch.float32)}
+        if self.taps > 1:
+            need["conv"] = StateNeed((self.taps, self.inner), self.dtype, by_position=True)
+        return need
+
+    def forward(self, h: torch.Tensor, ctx, view, residual32: torch.Tensor) -> None:
+        self._run(h, ctx, view, residual32, True)
+
+    def forward_store(self, h: torch.Tensor, ctx, view, out32: torch.Tensor) -> None:
+        """Stores the result instead of adding it."""
+        self._run(h, ctx, view, out32, False)
+
+    def _run(self, h, ctx, view, residual32, accumulate: bool) -> None:
+        T, ws = h.shape[0], ctx.workspace
+        inner, N, R = self.inner, self.N, self.R
+        proj = ws.buffer("ssm.in", (T, self.w_in.shape[0]), self.dtype)
+        kernels.linear(h, self.w_in, proj)
+        x = ws.buffer("ssm.conv", (T, inner), self.dtype)
+        ring = view["conv"].states if self.taps > 1 else None
+        kernels.short_conv(proj[:, :inner], self.w_conv, ring, ctx, x, act=True, bias=self.b_conv)
+        p = ws.buffer("ssm.x", (T, self.w_x.shape[0]), self.dtype)
+        kernels.linear(x, self.w_x, p)
+        dt = ws.buffer("ssm.dt", (T, inner), torch.float32)           # before bias and softplus, which the scan applies
+        kernels.linear(p[:, :R], self.w_dt, dt)
+        og = ws.buffer("ssm.gated", (T, inner), self.dtype)
+        kernels.selective_scan(x, dt, self.dt_bias, p[:, R:R + 2 * N], self.a, self.skip, proj[:, inner:2 * inner],
+                               view["state"].states, ctx, og, self.out_scale)
+        kernels.linear(og, self.w_o, residual32, accumulate=accumulate)
+
+
 class MLSTMMixer:
     graph_safe = True
     DEN_EPS = 1e-6            # added to the read-out's denominator
@@ -449,3 +530,4 @@ register_mixer("gated_delta", GatedDeltaMixer)
 register_mixer("parallel", ParallelMixer)
 register_mixer("ssd", SSDMixer)
 register_mixer("mlstm", MLSTMMixer)
+register_mixer("selective_ssm", SelectiveSSM)
