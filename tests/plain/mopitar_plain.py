@@ -105,6 +105,14 @@ def visible(i, j, window=0, keep_first=0):
     return i - j < window or j < keep_first
 
 
+def visible_keys(i, window=0, keep_first=0):
+    """The positions that ``visible`` lets the query at position i see, in ascending order."""
+    j = np.arange(i + 1)
+    if window <= 0:
+        return j
+    return j[(i - j < window) | (j < keep_first)]
+
+
 def attend(q, k, v, scale, *, softcap=0.0, sink=None, window=0, keep_first=0):
     """q [T, H, D], k [T, G, D], v [T, G, V] -> [T, H, V].  Scores (q . k) scale, optionally capped as
     cap tanh(s / cap); softmax over the visible keys, with exp(sink_h) as one more term of the
@@ -115,7 +123,7 @@ def attend(q, k, v, scale, *, softcap=0.0, sink=None, window=0, keep_first=0):
     for h in range(H):
         g = h // (H // G)
         for i in range(T):
-            js = [j for j in range(i + 1) if visible(i, j, window, keep_first)]
+            js = visible_keys(i, window, keep_first)
             s = (k[js, g, :] @ q[i, h, :]) * scale
             if softcap:
                 s = softcap * np.tanh(s / softcap)
@@ -278,15 +286,36 @@ def feed_forward(h, mlp, t, pre):
 
 
 # ---- the model --------------------------------------------------------------------------------------
-def forward(cfg, t, tokens, layers_out=None):
+def routing_margin(z, top, groups, keep):
+    """How clear one token's choice is: the smaller of (last group kept - best group left out) and (last
+    expert chosen - best eligible expert left out), each as a fraction of the larger of the two scores;
+    inf where nothing is left out."""
+    s = sigmoid(z)
+    E = len(s)
+    per = E // groups
+    gs = np.array([np.sort(s[g * per:(g + 1) * per])[::-1][:2].sum() for g in range(groups)])
+    order = np.argsort(-gs, kind="stable")
+    worst = np.inf
+    if keep < groups:
+        worst = (gs[order[keep - 1]] - gs[order[keep]]) / gs[order[keep - 1]]
+    ok = np.concatenate([s[g * per:(g + 1) * per] for g in sorted(order[:keep])])
+    ranked = -np.sort(-ok)
+    if top < len(ranked):
+        worst = min(worst, (ranked[top - 1] - ranked[top]) / ranked[top - 1])
+    return worst
+
+
+def forward(cfg, t, tokens, layers_out=None, watch=None):
     """Logits [T, vocab] of one sequence's tokens from its first.  ``layers_out``: a list that gets the
-    stream after every layer."""
+    stream after every layer.  ``watch(i, h)``: called with every layer's normed rows."""
     eps = float(cfg["norm"]["eps"])
     x = t["embed"][np.asarray(tokens)]
     kept = {}
     for i, layer in enumerate(cfg["layers"]):
         pre = f"l{i}."
         h = tanh_norm(x, t[pre + "norm1.alpha"], t[pre + "norm1"], t[pre + "norm1.b"])
+        if watch is not None:
+            watch(i, h)
         m = layer["mixer"]
         kind = layer["type"]
         if kind == "attention":
@@ -298,8 +327,10 @@ def forward(cfg, t, tokens, layers_out=None):
             y = two_branch_mixer(h, m, t, pre + "mix.", eps)
         else:
             raise ValueError(kind)
-        f = feed_forward(h, layer.get("mlp"), t, pre + "mlp.")
-        x = x + (y * t[pre + "ls1"] + f * t[pre + "ls2"])
+        y = y * t[pre + "ls1"]
+        if layer.get("mlp") is not None:
+            y = y + feed_forward(h, layer["mlp"], t, pre + "mlp.") * t[pre + "ls2"]
+        x = x + y
         if layers_out is not None:
             layers_out.append(x.copy())
     h = tanh_norm(x, t["final.norm.alpha"], t["final.norm"], t["final.norm.b"])
