@@ -17,6 +17,12 @@
 // to scratch; `attn_combine_kernel` merges a token's chunks in an order that depends on its
 // position only.
 //
+// Options of the extended entry point (`g2b_attn_decode_ex`): `softcap` > 0 turns a scaled score s into
+// softcap tanh(s / softcap); `keep_first` > 0 (with a window) keeps the keys at positions below it visible
+// behind the window, so a token's pages and chunks are then two ranges, walked in ascending order;
+// `v_heads` < nkv lets key head g read the values of head g mod v_heads (several score maps over one
+// set of values).
+//
 // Formula: src/l5_model.c:518, 559-577 of AnonymoDGH/gguf2bin.  Compiled per head size
 // (-DHD=64 or 128); the page size is 64 keys.
 #include "common.cuh"
@@ -92,20 +98,34 @@ __device__ __forceinline__ void load_q_tile(uint32_t (&qa)[KSTEPS][4], const bf1
   }
 }
 
-// One warp over the pages pg0, pg0 + stride, ... (n_pages of them, each holding a visible key):
-// K and V panels through the warp's two buffers; while it computes on K the V of the same page
-// is in flight, while it computes P.V the next K is.  The first K and V must have been issued
-// (one commit group each) before the call.
+// How a raw score becomes an exponent (log2 domain): times the scale, or capped first.
+struct ScoreMap {
+  float scale_log2;      // scale * log2(e)
+  float cap_in;          // scale / softcap (0: no cap)
+  float cap_log2;        // softcap * log2(e)
+  __device__ __forceinline__ float operator()(float s) const {
+    return cap_in > 0.f ? cap_log2 * tanhf(s * cap_in) : s * scale_log2;
+  }
+};
+
+// One warp over the pages pg_first + i * stride for every set bit i of `mask` (each holds a visible
+// key), in ascending order: K and V panels through the warp's two buffers; while it computes on K the
+// V of the same page is in flight, while it computes P.V the next K is.  The first page's K and V must
+// have been issued (one commit group each) before the call.  A key is visible if it is at most `pos`
+// and either at least `lo` or below `kept_end`.
 template <typename PanelOf>
 __device__ __forceinline__ void attend_pages(Partial &acc, const uint32_t (&qa)[KSTEPS][4], uint32_t k_smem,
-                                             uint32_t v_smem, int pg0, int stride, int n_pages, int pos, int lo,
-                                             float scale_log2, int lane, PanelOf panel_of) {
+                                             uint32_t v_smem, int pg_first, int stride, uint32_t mask, int pos, int lo,
+                                             int kept_end, ScoreMap score, int lane, PanelOf panel_of) {
   const int g = lane >> 2, c = lane & 3;
   (void)g;
   float (&o)[DTILES][4] = acc.o;
   float (&m)[2] = acc.m, (&l)[2] = acc.l;
-  for (int i = 0; i < n_pages; ++i) {
-    const int key0 = (pg0 + i * stride) * PAGE;
+  while (mask) {
+    const int i = __ffs(mask) - 1;
+    mask &= mask - 1;
+    const int nxt = mask ? __ffs(mask) - 1 : -1;
+    const int key0 = (pg_first + i * stride) * PAGE;
     cp_async_wait<1>();                    // this page's K has landed (its V may be in flight)
     __syncwarp();
     float s[PAGE / 8][4];
@@ -121,7 +141,7 @@ __device__ __forceinline__ void attend_pages(Partial &acc, const uint32_t (&qa)[
       }
     }
     __syncwarp();                          // every lane is done reading K
-    if (i + 1 < n_pages) load_panel(k_smem, panel_of(pg0 + (i + 1) * stride, 0), lane);
+    if (nxt >= 0) load_panel(k_smem, panel_of(pg_first + nxt * stride, 0), lane);
     cp_async_commit();
 
     // scale (log2 domain), mask, running maximum and sum
@@ -131,7 +151,7 @@ __device__ __forceinline__ void attend_pages(Partial &acc, const uint32_t (&qa)[
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int key = key0 + 8 * j + 2 * c + (e & 1);
-        const float v = (key <= pos && key >= lo) ? s[j][e] * scale_log2 : -INFINITY;
+        const float v = (key <= pos && (key >= lo || key < kept_end)) ? score(s[j][e]) : -INFINITY;
         s[j][e] = v;
         mx[e >> 1] = fmaxf(mx[e >> 1], v);
       }
@@ -176,7 +196,7 @@ __device__ __forceinline__ void attend_pages(Partial &acc, const uint32_t (&qa)[
       }
     }
     __syncwarp();
-    if (i + 1 < n_pages) load_panel(v_smem, panel_of(pg0 + (i + 1) * stride, 1), lane);
+    if (nxt >= 0) load_panel(v_smem, panel_of(pg_first + nxt * stride, 1), lane);
     cp_async_commit();
   }
   cp_async_wait<0>();
@@ -240,8 +260,8 @@ __global__ void __launch_bounds__(WARPS * 32)
 attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
                    const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
                    const int *__restrict__ page_table, int P, int nh, int nkv, int window,
-                   float scale_log2, float *__restrict__ part_o, float2 *__restrict__ part_ml,
-                   int n_chunks, int planes, int q_stride) {
+                   ScoreMap score, float *__restrict__ part_o, float2 *__restrict__ part_ml,
+                   int n_chunks, int planes, int q_stride, int keep_first, int v_heads) {
   pdl_launch();
   extern __shared__ __align__(128) unsigned char smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -259,10 +279,11 @@ attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
   // the batch's layout (which sequence, which pages) was copied to the device before the step's
   // first kernel was launched, so it may be read above the dependency line
   const int b = tok_seq[t];
+  const int vh = kvh % v_heads;                  // several key heads may share one value head
   auto panel_of = [&](int pg, int kv) {
     const int phys = page_table[(size_t)b * P + pg];
     // planes == 1: the page's one panel per kv head is read as keys and again as values
-    return cache + (((size_t)phys * planes + kv * (planes - 1)) * nkv + kvh) * panel_elems;
+    return cache + (((size_t)phys * planes + kv * (planes - 1)) * nkv + (kv && planes == 2 ? vh : kvh)) * panel_elems;
   };
 
   // Before the kernels in front of this one are done (they compute this token's query and
@@ -285,23 +306,22 @@ attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
   pdl_wait();
   const int pos = ld_volatile(tok_pos + t);
   const int lo = first_visible_key(pos, window);
-  if (key_begin > pos || key_begin + CHUNK_KEYS <= lo) return;     // no key of this chunk is seen (then nothing was fetched early)
+  const int kept_end = (keep_first > 0 && lo > 0) ? min(keep_first, lo) : 0;     // keys below it are seen behind the window
+  // no key of this chunk is seen (then nothing was fetched early)
+  if (key_begin > pos || (key_begin + CHUNK_KEYS <= lo && key_begin >= kept_end)) return;
 
-  // the pages of this warp: key_begin/PAGE + warp, + WARPS, ... that hold a visible key (the
-  // visible pages of a chunk are a contiguous range)
-  int pg0 = 0, n_pages = 0;
+  // the pages of this warp: key_begin/PAGE + warp, + WARPS, ... that hold a visible key
+  uint32_t mask = 0;
 #pragma unroll
   for (int i = 0; i < PAGES_PER_CTA / WARPS; ++i) {
     const int pg = first_page + warp + i * WARPS;
-    if (pg * PAGE <= pos && (pg + 1) * PAGE > lo) {
-      if (n_pages == 0) pg0 = pg;
-      ++n_pages;
-    }
+    if (pg * PAGE <= pos && ((pg + 1) * PAGE > lo || pg * PAGE < kept_end)) mask |= 1u << i;
   }
   if (!early) {
-    if (n_pages > 0) load_panel(k_smem, panel_of(pg0, 0), lane);
+    const int pg0 = first_page + warp + (mask ? __ffs(mask) - 1 : 0) * WARPS;
+    if (mask) load_panel(k_smem, panel_of(pg0, 0), lane);
     cp_async_commit();
-    if (n_pages > 0) load_panel(v_smem, panel_of(pg0, 1), lane);
+    if (mask) load_panel(v_smem, panel_of(pg0, 1), lane);
     cp_async_commit();
   }
 
@@ -309,7 +329,7 @@ attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
   load_q_tile(qa, q, t, q_stride, kvh, group, ht, g, c);
   Partial acc;
   clear_partial(acc);
-  attend_pages(acc, qa, k_smem, v_smem, pg0, WARPS, n_pages, pos, lo, scale_log2, lane, panel_of);
+  attend_pages(acc, qa, k_smem, v_smem, first_page + warp, WARPS, mask, pos, lo, kept_end, score, lane, panel_of);
   merge_warps(acc, reinterpret_cast<float *>(smem), WARPS, warp, lane);
   if (warp == 0) {
     float (&o)[DTILES][4] = acc.o;
@@ -337,7 +357,7 @@ __global__ void __launch_bounds__(COMBINE_WARPS * 32)
 attn_combine_kernel(const float *__restrict__ part_o, const float2 *__restrict__ part_ml,
                     const int *__restrict__ tok_pos, int nh, int window, int n_chunks,
                     bf16 *__restrict__ out, const float *__restrict__ sink,
-                    const bf16 *__restrict__ gate, int gate_stride) {
+                    const bf16 *__restrict__ gate, int gate_stride, int keep_first) {
   pdl_launch();
   pdl_wait();
   __shared__ float s_max[COMBINE_WARPS];
@@ -348,9 +368,15 @@ attn_combine_kernel(const float *__restrict__ part_o, const float2 *__restrict__
   const int pos = tok_pos[t];
   const int lo = first_visible_key(pos, window);
   const int c0 = lo / CHUNK_KEYS, c1 = pos / CHUNK_KEYS;
+  // with kept first tokens the chunks in front of the window's that hold one come first: the token's
+  // chunks are then number 0 .. nk - 1 and c0 .. c1, counted through as 0 .. total - 1
+  const int kept_end = (keep_first > 0 && lo > 0) ? min(keep_first, lo) : 0;
+  const int nk = min((kept_end + CHUNK_KEYS - 1) / CHUNK_KEYS, c0);
+  const int total = nk + (c1 - c0 + 1);
+  auto chunk_of = [&](int idx) { return idx < nk ? idx : c0 + idx - nk; };
   const float2 *ml = part_ml + th * n_chunks;
   float M = -INFINITY;
-  for (int i = c0 + (int)threadIdx.x; i <= c1; i += COMBINE_WARPS * 32) M = fmaxf(M, ml[i].x);
+  for (int i = (int)threadIdx.x; i < total; i += COMBINE_WARPS * 32) M = fmaxf(M, ml[chunk_of(i)].x);
   M = warp_max(M);
   if (lane == 0) s_max[warp] = M;
   __syncthreads();
@@ -361,20 +387,20 @@ attn_combine_kernel(const float *__restrict__ part_o, const float2 *__restrict__
   // eight chunks' loads in flight at a time (a token far into its sequence has hundreds of chunks,
   // and one load after the other cost 20 us at 65,536 keys); they are added in the same order
   constexpr int AHEAD = 8;
-  for (int i0 = c0 + warp; i0 <= c1; i0 += AHEAD * COMBINE_WARPS) {
+  for (int i0 = warp; i0 < total; i0 += AHEAD * COMBINE_WARPS) {
     float2 mlv[AHEAD];
     float4 ov[AHEAD];
 #pragma unroll
     for (int u = 0; u < AHEAD; ++u) {
-      const int i = i0 + u * COMBINE_WARPS;
-      if (i <= c1) {
+      if (i0 + u * COMBINE_WARPS < total) {
+        const int i = chunk_of(i0 + u * COMBINE_WARPS);
         mlv[u] = ml[i];
         if (active) ov[u] = *reinterpret_cast<const float4 *>(part_o + (th * n_chunks + i) * HD + 4 * lane);
       }
     }
 #pragma unroll
     for (int u = 0; u < AHEAD; ++u) {
-      if (i0 + u * COMBINE_WARPS <= c1) {
+      if (i0 + u * COMBINE_WARPS < total) {
         const float w = fast_exp2(mlv[u].x - M);
         if (active) {
           num.x = fmaf(w, ov[u].x, num.x); num.y = fmaf(w, ov[u].y, num.y);
@@ -407,13 +433,17 @@ attn_combine_kernel(const float *__restrict__ part_o, const float2 *__restrict__
 // kernels move tok_pos while this one may already have started must keep to what the library
 // does: positions grow, and shrink by at most one (a step taken back) between two launches.
 // With ordinary launches (the default of a freshly loaded object) there is no such rule.
-extern "C" int g2b_attn_decode(const void *q, void *out, const void *cache, const int *tok_pos,
-                               const int *tok_seq, const int *page_table, int P, int T, int nh,
-                               int nkv, int hd, int page_size, int window, float scale,
-                               int max_kv_len, float *part_o, float *part_ml,
-                               const float *sink, int planes, int q_stride, const void *gate,
-                               int gate_stride, cudaStream_t stream) {
+extern "C" int g2b_attn_decode_ex(const void *q, void *out, const void *cache, const int *tok_pos,
+                                  const int *tok_seq, const int *page_table, int P, int T, int nh,
+                                  int nkv, int hd, int page_size, int window, float scale,
+                                  int max_kv_len, float *part_o, float *part_ml,
+                                  const float *sink, int planes, int q_stride, const void *gate,
+                                  int gate_stride, float softcap, int keep_first, int v_heads, cudaStream_t stream) {
   if (T <= 0) return 0;
+  if (v_heads <= 0) v_heads = nkv;
+  if (nkv > 0 && (v_heads > nkv || nkv % v_heads)) G2B_REFUSE("attn_decode: %d key heads on %d value heads", nkv, v_heads);
+  if (softcap < 0.f || keep_first < 0 || (keep_first > 0 && window <= 0))
+    G2B_REFUSE("attn_decode: a cap of %g, %d first tokens kept with a window of %d", softcap, keep_first, window);
   if (planes != 1 && planes != 2) G2B_REFUSE("attn_decode: %d panels per page and kv head (1 or 2)", planes);
   if (q_stride < nh * hd || q_stride % 2) G2B_REFUSE("attn_decode: query rows %d elements apart", q_stride);
   if (hd != HD) G2B_REFUSE("attn_decode: built for head_dim %d, got %d", HD, hd);
@@ -436,13 +466,25 @@ extern "C" int g2b_attn_decode(const void *q, void *out, const void *cache, cons
   dim3 grid(n_chunks, nkv * head_tiles, T);
   g2b_launch(attn_decode_kernel, dim3(grid), dim3(WARPS * 32), smem, stream, 
       (const bf16 *)q, (const bf16 *)cache, tok_pos, tok_seq, page_table, P, nh, nkv, window,
-      scale * LOG2E, part_o, (float2 *)part_ml, n_chunks, planes, q_stride);
+      ScoreMap{scale * LOG2E, softcap > 0.f ? scale / softcap : 0.f, softcap * LOG2E}, part_o, (float2 *)part_ml,
+      n_chunks, planes, q_stride, keep_first, v_heads);
   int rc = g2b_check_launch("attn_decode");
   if (rc) return rc;
   g2b_launch(attn_combine_kernel, dim3((unsigned)((size_t)T * nh)), dim3(COMBINE_WARPS * 32), 0, stream, 
       part_o, (const float2 *)part_ml, tok_pos, nh, window, n_chunks, (bf16 *)out, sink, (const bf16 *)gate,
-      gate_stride);
+      gate_stride, keep_first);
   return g2b_check_launch("attn_combine");
+}
+
+// The entry point without the options above.
+extern "C" int g2b_attn_decode(const void *q, void *out, const void *cache, const int *tok_pos,
+                               const int *tok_seq, const int *page_table, int P, int T, int nh,
+                               int nkv, int hd, int page_size, int window, float scale,
+                               int max_kv_len, float *part_o, float *part_ml,
+                               const float *sink, int planes, int q_stride, const void *gate,
+                               int gate_stride, cudaStream_t stream) {
+  return g2b_attn_decode_ex(q, out, cache, tok_pos, tok_seq, page_table, P, T, nh, nkv, hd, page_size, window, scale,
+                            max_kv_len, part_o, part_ml, sink, planes, q_stride, gate, gate_stride, 0.f, 0, 0, stream);
 }
 
 extern "C" int g2b_attn_decode_chunk_keys() { return CHUNK_KEYS; }

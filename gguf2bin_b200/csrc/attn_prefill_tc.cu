@@ -33,6 +33,13 @@
 // Every mbarrier wait is bounded; a wait that gives up records a code in `*status`, all roles
 // fall through to the common exit and the tensor memory is freed.
 //
+// Options of the extended entry point (`g2b_attn_prefill_tc_ex`).  `softcap` > 0: a scaled score s becomes
+// softcap tanh(s / softcap) before the mask, with tanh as 1 - 2 / (1 + 2^(2 s log2 e / softcap)) from the fast
+// exponential and division (a few parts in ten million of the cap); the kernel's scale is then that of the
+// logarithm alone.  `keep_first` > 0 (with a window): the keys below that position stay visible behind the
+// window; the pages that hold them and lie in front of the window's first page take the panels in front of
+// the window's pages.  `v_heads` < nkv: key head g reads the values of head g mod v_heads.
+//
 // Pooled blocks (the second instantiation, `POOLED`): with a window and `pool` > 0 a query at
 // position p also sees one key and value for every block of `pool` positions that lies wholly
 // before its window: block j if j pool + pool - 1 <= p - window.  They come from a second store
@@ -136,7 +143,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                        int nh, int nkv, int window, float scale_log2, int first_wave,
                        int *__restrict__ status, const float *__restrict__ sink, int planes,
                        const bf16 *__restrict__ gate, int gate_stride, const bf16 *__restrict__ pooled,
-                       int pool, int pool_rows) {
+                       int pool, int pool_rows, float cap_in2, float cap, int keep_first, int v_heads) {
   pdl_launch();
   // The swizzled panels need 1024-byte alignment.  The kernel has no static shared memory, so
   // the dynamic part starts at the aligned base of the window; checked rather than assumed.
@@ -191,12 +198,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   const int4 tile = tiles[item / nh];
   const int b = tile.x, t0 = tile.y, n_rows = tile.z, pos0 = tile.w;
   const int h = item % nh, kvh = h / (nh / nkv);
+  const int vh = planes == 2 ? kvh % v_heads : kvh;     // several key heads may share one value head
   const int first_page = first_visible_key(pos0, window) / PAGE;
   const int last_page = (pos0 + n_rows - 1) / PAGE;
+  // pages in front of the window's first that hold kept first tokens: they come before the window's pages
+  const int n_kp = keep_first > 0 ? min((keep_first + PAGE - 1) / PAGE, first_page) : 0;
+  auto page_of = [&](int i) { return i < n_kp ? i : first_page + (i - n_kp); };
   // panels: first the pooled blocks that the tile's last row sees, 64 a panel, then the window's pages
   const int nb_max = POOLED ? max(0, pos0 + n_rows - window) / pool : 0;
   const int n_pp = (nb_max + PAGE - 1) / PAGE;
-  const int n_pages = n_pp + last_page - first_page + 1;
+  const int n_pages = n_pp + n_kp + last_page - first_page + 1;
 
   if (warp == SOFTMAX_WARPS) {
     // without pooled blocks one thread issues every copy; with them the whole warp goes through the
@@ -209,7 +220,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
           tma_load_2d(smem_addr(q_smem + sub * Q_SUB_BYTES), &map_q, h * HD + 64 * sub, t0, q_full);
       }
       const int *pt_seq = page_table + (size_t)b * P;
-      const int *pt = pt_seq + first_page;
       // whether the stage is free again; with pooled blocks thread 0 waits and tells the others
       auto stage_free = [&](uint32_t bar, uint32_t parity) -> bool {
         if (!POOLED) return mbar_wait(bar, parity);
@@ -244,7 +254,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         if (POOLED && i < n_pp) {
           gather(k_smem + s * KV_BYTES, i, 0, k_full0 + 8 * s);
         } else if (lane == 0) {
-          const int row = ((pt[i - n_pp] * planes + 0) * nkv + kvh) * PAGE;
+          const int row = ((pt_seq[page_of(i - n_pp)] * planes + 0) * nkv + kvh) * PAGE;
           const uint32_t dst = smem_addr(k_smem + s * KV_BYTES);
           mbar_expect_tx(k_full0 + 8 * s, KV_BYTES);
 #pragma unroll
@@ -260,7 +270,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         if (POOLED && i < n_pp) {
           gather(v_smem + s * KV_BYTES, i, 1, v_full0 + 8 * s);
         } else if (lane == 0) {
-          const int row = ((pt[i - n_pp] * planes + (planes - 1)) * nkv + kvh) * PAGE;      // one panel: it is keys and values
+          const int row = ((pt_seq[page_of(i - n_pp)] * planes + (planes - 1)) * nkv + vh) * PAGE;      // one panel: it is keys and values
           const uint32_t dst = smem_addr(v_smem + s * KV_BYTES);
           mbar_expect_tx(v_full0 + 8 * s, KV_BYTES);
 #pragma unroll
@@ -375,7 +385,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       TOCK(6, t_ld);
       // a pooled panel counts in blocks: block j is seen by a row while j < the row's block count
       const bool in_pool = POOLED && i < n_pp;
-      const int key0 = in_pool ? i * PAGE : (first_page + i - n_pp) * PAGE;
+      const int key0 = in_pool ? i * PAGE : page_of(i - n_pp) * PAGE;
+      if (cap > 0.f) {                             // capped scores: cap tanh(s scale / cap), scale_log2 is log2(e) alone
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          sr[j] = __float_as_uint(fmaf(-2.f * cap, __fdividef(1.f, 1.f + ex2(__uint_as_float(sr[j]) * cap_in2)), cap));
+      }
       const int hi_a = in_pool ? nb_a - 1 : pos_a, hi_b = in_pool ? nb_b - 1 : pos_b;
       const int lw_a = in_pool ? 0 : lo_a, lw_b = in_pool ? 0 : lo_b;
       TICK(t_mx);
@@ -391,8 +406,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int key = key0 + 8 * j + 2 * c + e;
-            if (key > hi_a || key < lw_a) sr[4 * j + e] = 0xff800000u;           // -inf
-            if (key > hi_b || key < lw_b) sr[4 * j + 2 + e] = 0xff800000u;
+            const bool kept = !in_pool && key < keep_first;                       // seen behind the window
+            if (key > hi_a || (key < lw_a && !kept)) sr[4 * j + e] = 0xff800000u;           // -inf
+            if (key > hi_b || (key < lw_b && !kept)) sr[4 * j + 2 + e] = 0xff800000u;
           }
       }
       float mxa[2] = {-INFINITY, -INFINITY}, mxb[2] = {-INFINITY, -INFINITY};       // short chains
@@ -528,8 +544,16 @@ static int launch_prefill_tc(const void *q, void *out, const void *cache, long l
                              int T, int nh, int nkv, int hd, int page_size, int window,
                              float scale, const float *sink, int planes, int q_stride,
                              const void *gate, int gate_stride, const void *pooled, int pool, int pool_rows,
-                             int *status, cudaStream_t stream) {
+                             int *status, cudaStream_t stream, float softcap = 0.f, int keep_first = 0, int v_heads = 0) {
   if (n_tiles <= 0) return 0;
+  if (v_heads <= 0) v_heads = nkv;
+  if (nkv > 0 && (v_heads > nkv || nkv % v_heads)) G2B_REFUSE("attn_prefill_tc: %d key heads on %d value heads", nkv, v_heads);
+  if (softcap < 0.f || keep_first < 0 || (keep_first > 0 && (window <= 0 || pooled)) || (softcap > 0.f && pooled))
+    G2B_REFUSE("attn_prefill_tc: a cap of %g, %d first tokens kept with a window of %d%s", softcap, keep_first, window,
+               pooled ? " and pooled blocks" : "");
+  // with a cap the kernel turns raw scores into capped ones itself; what is left of the scale is log2(e)
+  const float scale_log2 = softcap > 0.f ? LOG2E : scale * LOG2E;
+  const float cap_in2 = softcap > 0.f ? 2.f * LOG2E * scale / softcap : 0.f;
   if (hd != HD) G2B_REFUSE("attn_prefill_tc: built for head_dim %d, got %d", HD, hd);
   if (page_size != PAGE) G2B_REFUSE("attn_prefill_tc: page size must be %d, got %d", PAGE, page_size);
   if (nkv <= 0 || nh % nkv) G2B_REFUSE("attn_prefill_tc: %d heads are not a multiple of %d kv heads", nh, nkv);
@@ -568,12 +592,12 @@ static int launch_prefill_tc(const void *q, void *out, const void *cache, long l
   }
   if (pooled)
     g2b_launch(attn_prefill_tc_kernel<true>, dim3((unsigned)n_tiles * nh), dim3(THREADS), SMEM_TOTAL, stream, mq, mkv,
-               (bf16 *)out, (const int4 *)tiles, page_table, P, nh, nkv, window, scale * LOG2E, n_sms, status, sink,
-               planes, (const bf16 *)gate, gate_stride, (const bf16 *)pooled, pool, pool_rows);
+               (bf16 *)out, (const int4 *)tiles, page_table, P, nh, nkv, window, scale_log2, n_sms, status, sink,
+               planes, (const bf16 *)gate, gate_stride, (const bf16 *)pooled, pool, pool_rows, 0.f, 0.f, 0, v_heads);
   else
     g2b_launch(attn_prefill_tc_kernel<false>, dim3((unsigned)n_tiles * nh), dim3(THREADS), SMEM_TOTAL, stream, mq, mkv,
-               (bf16 *)out, (const int4 *)tiles, page_table, P, nh, nkv, window, scale * LOG2E, n_sms, status, sink,
-               planes, (const bf16 *)gate, gate_stride, (const bf16 *)nullptr, 0, 0);
+               (bf16 *)out, (const int4 *)tiles, page_table, P, nh, nkv, window, scale_log2, n_sms, status, sink,
+               planes, (const bf16 *)gate, gate_stride, (const bf16 *)nullptr, 0, 0, cap_in2, softcap, keep_first, v_heads);
   return g2b_check_launch("attn_prefill_tc");
 }
 
@@ -584,6 +608,18 @@ extern "C" int g2b_attn_prefill_tc(const void *q, void *out, const void *cache, 
                                    const void *gate, int gate_stride, int *status, cudaStream_t stream) {
   return launch_prefill_tc(q, out, cache, n_cache_pages, tiles, n_tiles, page_table, P, T, nh, nkv, hd, page_size,
                            window, scale, sink, planes, q_stride, gate, gate_stride, nullptr, 0, 0, status, stream);
+}
+
+// With capped scores, kept first tokens behind the window and key heads that share value heads.
+extern "C" int g2b_attn_prefill_tc_ex(const void *q, void *out, const void *cache, long long n_cache_pages,
+                                      const int *tiles, int n_tiles, const int *page_table, int P,
+                                      int T, int nh, int nkv, int hd, int page_size, int window,
+                                      float scale, const float *sink, int planes, int q_stride,
+                                      const void *gate, int gate_stride, float softcap, int keep_first, int v_heads,
+                                      int *status, cudaStream_t stream) {
+  return launch_prefill_tc(q, out, cache, n_cache_pages, tiles, n_tiles, page_table, P, T, nh, nkv, hd, page_size,
+                           window, scale, sink, planes, q_stride, gate, gate_stride, nullptr, 0, 0, status, stream,
+                           softcap, keep_first, v_heads);
 }
 
 // The same over a window of tokens and, in front of it, the pooled blocks of `pool` positions.

@@ -140,7 +140,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                        const int4 *__restrict__ tiles, const int *__restrict__ page_table, int P,
                        int nh, int nkv, int window, float scale_log2, int *__restrict__ status,
                        const float *__restrict__ sink, int planes,
-                       const bf16 *__restrict__ gate, int gate_stride) {
+                       const bf16 *__restrict__ gate, int gate_stride, float cap_in2, float cap, int keep_first,
+                       int v_heads) {
   pdl_launch();
   // The swizzled panels need 1024-byte alignment.  The kernel has no static shared memory, so
   // the dynamic part starts at the aligned base of the window; checked rather than assumed.
@@ -191,9 +192,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   const int4 tile = tiles[item / nh];
   const int b = tile.x, t0 = tile.y, n_rows = tile.z, pos0 = tile.w;
   const int h = item % nh, kvh = h / (nh / nkv);
+  const int vh = planes == 2 ? kvh % v_heads : kvh;     // several key heads may share one value head
   const int first_page = first_visible_key(pos0, window) / PAGE;
   const int last_page = (pos0 + n_rows - 1) / PAGE;
-  const int n_pages = last_page - first_page + 1;
+  // pages in front of the window's first that hold kept first tokens: they come before the window's pages
+  const int n_kp = keep_first > 0 ? min((keep_first + PAGE - 1) / PAGE, first_page) : 0;
+  auto page_of = [&](int i) { return i < n_kp ? i : first_page + (i - n_kp); };
+  const int n_pages = n_kp + last_page - first_page + 1;
 
   if (warp == SOFTMAX_WARPS) {
     if (lane == 0 && PRODUCER_RUNS) {
@@ -201,11 +206,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
       for (int sub = 0; sub < SUBS; ++sub)
         tma_load_2d(smem_addr(q_smem + sub * Q_SUB_BYTES), &map_q, h * HD + 64 * sub, t0, q_full);
-      const int *pt = page_table + (size_t)b * P + first_page;
+      const int *pt_seq = page_table + (size_t)b * P;
       auto load_k = [&](int i) -> bool {
         const int s = i % K_STAGES;
         if (i >= K_STAGES && !mbar_wait(k_empty0 + 8 * s, ((i / K_STAGES) - 1) & 1)) return false;
-        const int row = ((pt[i] * planes + 0) * nkv + kvh) * PAGE;
+        const int row = ((pt_seq[page_of(i)] * planes + 0) * nkv + kvh) * PAGE;
         const uint32_t dst = smem_addr(k_smem + s * KV_BYTES);
         mbar_expect_tx(k_full0 + 8 * s, KV_BYTES);
 #pragma unroll
@@ -216,7 +221,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       auto load_v = [&](int i) -> bool {
         const int s = i % V_STAGES;
         if (i >= V_STAGES && !mbar_wait(v_empty0 + 8 * s, ((i / V_STAGES) - 1) & 1)) return false;
-        const int row = ((pt[i] * planes + (planes - 1)) * nkv + kvh) * PAGE;      // one panel: it is keys and values
+        const int row = ((pt_seq[page_of(i)] * planes + (planes - 1)) * nkv + vh) * PAGE;      // one panel: it is keys and values
         const uint32_t dst = smem_addr(v_smem + s * KV_BYTES);
         mbar_expect_tx(v_full0 + 8 * s, KV_BYTES);
 #pragma unroll
@@ -325,7 +330,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       tmem_ld_wait();
       TOCK(8, t_ld);
       TICK(t_mx);
-      const int key0 = (first_page + i) * PAGE;
+      const int key0 = page_of(i) * PAGE;
+      if (cap > 0.f) {                             // capped scores: cap tanh(s scale / cap), scale_log2 is log2(e) alone
+#pragma unroll
+        for (int j = 0; j < 64; ++j)
+          sr[j] = __float_as_uint(fmaf(-2.f * cap, __fdividef(1.f, 1.f + ex2(__uint_as_float(sr[j]) * cap_in2)), cap));
+      }
       // raw scores stay in sr; the scale (> 0) is applied to the maximum and inside the exponent.
       // Only pages that cross the limits of the warp's rows are masked (warp-uniform test).
       const int warp_pos_min = pos0 + (warp & 3) * 32, warp_pos_max = warp_pos_min + 31;
@@ -334,7 +344,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       if (partial) {
 #pragma unroll
         for (int j = 0; j < 64; ++j)
-          if (key0 + j > pos || key0 + j < lo) sr[j] = 0xff800000u;                 // -inf
+          if (key0 + j > pos || (key0 + j < lo && key0 + j >= keep_first)) sr[j] = 0xff800000u;      // -inf
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};                  // short chains
 #pragma unroll
@@ -453,12 +463,25 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 
 // q, out [T, nh*HD] bfloat16; cache [n_pages][2][nkv][64][HD] bfloat16 of one layer;
 // tiles [n_tiles][4] int32 = {sequence, first token, rows (<= 128), position of row 0}.
-extern "C" int g2b_attn_prefill_tc(const void *q, void *out, const void *cache, long long n_cache_pages,
-                                   const int *tiles, int n_tiles, const int *page_table, int P,
-                                   int T, int nh, int nkv, int hd, int page_size, int window,
-                                   float scale, const float *sink, int planes, int q_stride,
-                                   const void *gate, int gate_stride, int *status, cudaStream_t stream) {
+// `softcap` > 0: a scaled score s becomes softcap tanh(s / softcap) before the mask (tanh from the fast
+// exponential and division).  `keep_first` > 0 (with a window): the keys below that position stay visible behind
+// the window; their pages in front of the window's first come first.  `v_heads` < nkv: key head g reads the
+// values of head g mod v_heads.
+extern "C" int g2b_attn_prefill_tc_ex(const void *q, void *out, const void *cache, long long n_cache_pages,
+                                      const int *tiles, int n_tiles, const int *page_table, int P,
+                                      int T, int nh, int nkv, int hd, int page_size, int window,
+                                      float scale, const float *sink, int planes, int q_stride,
+                                      const void *gate, int gate_stride, float softcap, int keep_first, int v_heads,
+                                      int *status, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
+  if (v_heads <= 0) v_heads = nkv;
+  if (nkv > 0 && (v_heads > nkv || nkv % v_heads))
+    G2B_REFUSE("attn_prefill_tc (split): %d key heads on %d value heads", nkv, v_heads);
+  if (softcap < 0.f || keep_first < 0 || (keep_first > 0 && window <= 0))
+    G2B_REFUSE("attn_prefill_tc (split): a cap of %g, %d first tokens kept with a window of %d", softcap, keep_first, window);
+  // with a cap the kernel turns raw scores into capped ones itself; what is left of the scale is log2(e)
+  const float scale_log2 = softcap > 0.f ? LOG2E : scale * LOG2E;
+  const float cap_in2 = softcap > 0.f ? 2.f * LOG2E * scale / softcap : 0.f;
   if (hd != HD) G2B_REFUSE("attn_prefill_tc (split): built for head_dim %d, got %d", HD, hd);
   if (page_size != PAGE) G2B_REFUSE("attn_prefill_tc (split): page size must be %d, got %d", PAGE, page_size);
   if (nkv <= 0 || nh % nkv) G2B_REFUSE("attn_prefill_tc (split): %d heads are not a multiple of %d kv heads", nh, nkv);
@@ -485,8 +508,19 @@ extern "C" int g2b_attn_prefill_tc(const void *q, void *out, const void *cache, 
     if (cfg_dev >= 0) configured.value[cfg_dev] = 1;
   }
   g2b_launch(attn_prefill_tc_kernel, dim3((unsigned)n_tiles * nh), dim3(THREADS), SMEM_TOTAL, stream, mq, mkv,
-             (bf16 *)out, (const int4 *)tiles, page_table, P, nh, nkv, window, scale * LOG2E, status, sink, planes, (const bf16 *)gate, gate_stride);
+             (bf16 *)out, (const int4 *)tiles, page_table, P, nh, nkv, window, scale_log2, status, sink, planes,
+             (const bf16 *)gate, gate_stride, cap_in2, softcap, keep_first, v_heads);
   return g2b_check_launch("attn_prefill_tc (split)");
+}
+
+// The entry point without the options above.
+extern "C" int g2b_attn_prefill_tc(const void *q, void *out, const void *cache, long long n_cache_pages,
+                                   const int *tiles, int n_tiles, const int *page_table, int P,
+                                   int T, int nh, int nkv, int hd, int page_size, int window,
+                                   float scale, const float *sink, int planes, int q_stride,
+                                   const void *gate, int gate_stride, int *status, cudaStream_t stream) {
+  return g2b_attn_prefill_tc_ex(q, out, cache, n_cache_pages, tiles, n_tiles, page_table, P, T, nh, nkv, hd, page_size,
+                                window, scale, sink, planes, q_stride, gate, gate_stride, 0.f, 0, 0, status, stream);
 }
 
 extern "C" int g2b_attn_prefill_tc_tile_rows() { return BM; }

@@ -308,8 +308,9 @@ def attention_bf16(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page
                    scale, sink=None, planes: int = 2, gate=None, chunk: int = 0, softcap: float = 0.0,
                    keep_first: int = 0, v_heads: int = 0) -> bool:
     """``chunk`` > 0 (keys of the token's own chunk only) reaches the kernels as a negative window."""
-    if softcap or keep_first or (v_heads and v_heads != n_kv_heads):
-        return False              # capped scores, kept first tokens and shared value heads: the 32-bit kernel
+    extra = bool(softcap or keep_first or (v_heads and v_heads != n_kv_heads))
+    if extra and (chunk or planes != 2):
+        return False
     if chunk:
         if window:
             return False
@@ -324,13 +325,13 @@ def attention_bf16(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page
         return False
     if ctx.all_single:
         attn_decode(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window, scale,
-                    sink=sink, planes=planes, gate=gate)
+                    sink=sink, planes=planes, gate=gate, softcap=softcap, keep_first=keep_first, v_heads=v_heads)
         return True
     if USE_TC_ATTENTION and getattr(ctx, "attn_tiles_wide", None) is not None and ctx.n_attn_tiles_wide > 0:
         attn_prefill_tc(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window, scale,
-                        sink=sink, planes=planes, gate=gate)
+                        sink=sink, planes=planes, gate=gate, softcap=softcap, keep_first=keep_first, v_heads=v_heads)
         return True
-    if sink is not None or planes != 2 or gate is not None or q.stride(0) != n_heads * head_dim or window < 0:
+    if sink is not None or planes != 2 or gate is not None or q.stride(0) != n_heads * head_dim or window < 0 or extra:
         # the mma.sync prompt kernel knows none of these
         return False
     if getattr(ctx, "attn_tiles", None) is not None and ctx.n_attn_tiles > 0:
@@ -378,7 +379,8 @@ USE_TC_ATTENTION = True      # prompt attention on tcgen05 (else the mma.sync ke
 
 
 def attn_prefill_tc(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
-                    scale, defines=(), split=None, sink=None, planes: int = 2, gate=None) -> None:
+                    scale, defines=(), split=None, sink=None, planes: int = 2, gate=None, softcap: float = 0.0,
+                    keep_first: int = 0, v_heads: int = 0) -> None:
     """Prompt attention on the tcgen05 tensor cores over the step's 128-row query tiles.  Two
     kernels with the same interface: two CTAs per SM, a tile each (``attn_prefill_tc.cu``), and
     one CTA per SM whose two softmax groups share a tile's pages (``attn_prefill_tc_split.cu``;
@@ -391,14 +393,18 @@ def attn_prefill_tc(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, pag
     if split is None:
         items, sms = ctx.n_attn_tiles_wide * n_heads, _sm_count(q.device)
         split = items <= sms or (items <= 2 * sms and getattr(ctx, "max_kv_len", 0) >= 1024)
-    f = _fn("attn_prefill_tc_split.cu" if split else "attn_prefill_tc.cu", "g2b_attn_prefill_tc",
+    # capped scores (softcap * tanh(score / softcap)), the first ``keep_first`` positions visible behind a
+    # window, and key head g on value head g mod ``v_heads`` are options of the extended entry point
+    f = _fn("attn_prefill_tc_split.cu" if split else "attn_prefill_tc.cu", "g2b_attn_prefill_tc_ex",
             [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
-             c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p],
+             c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_void_p, c_int, c_float, c_int, c_int,
+             c_void_p, c_void_p],
             defines=(f"HD={head_dim}",) + tuple(defines))
     _call(f, _ptr(q), _ptr(out), _ptr(cache_pages), cache_pages.shape[0], _ptr(ctx.attn_tiles_wide),
           ctx.n_attn_tiles_wide, _ptr(ctx.page_table), ctx.page_table.shape[1], q.shape[0], n_heads,
           n_kv_heads, head_dim, page_size, window, scale, _ptr(sink), planes, q.stride(0), _ptr(gate),
-          gate.stride(0) if gate is not None else 0, _ptr(_status_word(q.device)), _stream())
+          gate.stride(0) if gate is not None else 0, float(softcap), int(keep_first), int(v_heads),
+          _ptr(_status_word(q.device)), _stream())
 
 
 def attn_prefill(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
@@ -436,7 +442,8 @@ def decode_chunk_pages(units: int, pages: int, head_dim: int, slots: int) -> int
 
 
 def attn_decode(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
-                scale, fine=None, pages=None, sink=None, planes: int = 2, gate=None) -> None:
+                scale, fine=None, pages=None, sink=None, planes: int = 2, gate=None, softcap: float = 0.0,
+                keep_first: int = 0, v_heads: int = 0) -> None:
     """One token per sequence: split-key attention with partial results in scratch memory
     and a combine pass.  A CTA takes a chunk of keys of one kv head: 256 as a rule, 128, 384 or
     512 where ``decode_chunk_pages`` says so (``fine`` = 128; ``pages`` = pages of 64 keys per
@@ -458,13 +465,14 @@ def attn_decode(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_si
     ws = ctx.workspace
     part_o = ws.buffer("attn.part_o", (T * n_heads * n_chunks * head_dim,), torch.float32)
     part_ml = ws.buffer("attn.part_ml", (T * n_heads * n_chunks * 2,), torch.float32)
-    f = _fn("attn_decode.cu", "g2b_attn_decode",
+    f = _fn("attn_decode.cu", "g2b_attn_decode_ex",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
              c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
-             c_int, c_void_p],
+             c_int, c_float, c_int, c_int, c_void_p],
             defines=defines)
     _call(f, _ptr(q), _ptr(out), _ptr(cache_pages), _ptr(ctx.tok_pos), _ptr(ctx.tok_seq),
           _ptr(ctx.page_table), ctx.page_table.shape[1], T, n_heads, n_kv_heads, head_dim,
           page_size, window, scale, int(ctx.max_kv_len), _ptr(part_o), _ptr(part_ml), _ptr(sink), planes,
-          q.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, _stream())
+          q.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, float(softcap), int(keep_first),
+          int(v_heads), _stream())
     kernels.count_launches(1)                      # the attention and the merge of its chunks
