@@ -2,7 +2,7 @@
 """Decode and prefill throughput of gguf2bin_b200 on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload decode|ragged8|b64|senotar|levolix|sominex] [--batch B] [--layers L] [--context C]
+                    [--workload decode|ragged8|b64|senotar|levolix|sominex|mopitar] [--batch B] [--layers L] [--context C]
                     [--no-points] [--sizes 0.6b|8b|14b]
 
 The default run has the layer sizes of Qwen3-0.6B (28 layers, width 1024, 16/8 heads of
@@ -46,6 +46,12 @@ that each reaches.  It prints one JSON line of its own shape.
 chunked attention beside the gated delta rule, routed experts): active parameters per token within
 a few per cent of the Qwen3 model's; the decode roofline counts every expert matrix once, the
 states read and written, and the keys and values of a request's current chunk.
+
+``--workload mopitar`` sets Mopitar (two score maps per head behind a window with kept first tokens, capped
+attention with a sink beside a selective state-space branch, layers that borrow keys and values, routed
+experts in groups) beside Sominex, the library's closest design (one norm in front of both sublayers,
+windowed attention, a state-space mixer, routed experts with a shared one), at equal width, layer count,
+vocabulary and, within a few per cent, active parameters.
 
 Peaks come from MEASURED_PEAKS.json beside this file when present, else from the
 fallback figures 6.65 TB/s and 1.59 PFLOP/s.  Inputs are synthetic.  Between timed steps
@@ -574,6 +580,130 @@ def sominex_comparison(a, pk) -> int:
     return 0
 
 
+# ---- Mopitar beside Sominex at equal sizes ------------------------------------------------------
+def mopitar_config(width, layers, vocab) -> dict:
+    """Two maps behind a window, the two-branch mixer, capped attention in turn; the second capped attention
+    borrows the first one's keys and values; dense and routed feed-forwards in turn."""
+    H = width // 128
+    G = max(H // 4, 1)
+    out, lender = [], None
+    dense = dict(kind="dense", ff=9 * width // 2)
+    routed = dict(kind="moe", expert=dict(ff=3 * width // 4), shared=dict(ff=3 * width // 2),
+                  router=dict(experts=16, top=2, groups=dict(count=4, keep=2)))
+    for i in range(layers):
+        mlp = routed if i % 2 else dense
+        if i % 3 == 0:
+            scaling = dict(factor=4.0, original=2048, fast=32.0, slow=1.0)
+            out.append(dict(type="attention_2", mlp=mlp,
+                            mixer=dict(heads=H, kv_heads=G, dim=128, vdim=128, scale=128 ** -0.5, diff=0.6,
+                                       mask=dict(size=512, keep_first=4), rot=dict(dims=64, base=1e6, scaling=scaling))))
+        elif i % 3 == 1:
+            left = dict(heads=max(H // 2, 1), kv_heads=max(G // 2, 1), dim=128, vdim=128, scale=0.09, softcap=50.0,
+                        rot=dict(dims=128, base=5e5))
+            right = dict(inner=2 * width, state=16, dt_rank=max(width // 16, 8), conv=4)
+            out.append(dict(type="parallel", mlp=mlp, mixer=dict(left=left, right=right, left_scale=0.8, right_scale=0.5)))
+        else:
+            m = dict(heads=H, kv_heads=G, dim=128, vdim=128, scale=128 ** -0.5, softcap=30.0, rot=dict(dims=128, base=1e4))
+            if lender is not None:
+                m["kv_from"] = lender
+            else:
+                lender = i
+            out.append(dict(type="attention", mlp=mlp, mixer=m))
+    return dict(architecture="Mopitar", width=width, vocab=vocab, norm=dict(eps=1e-6), layers=out)
+
+
+def mopitar_bytes_and_flops(cfg: dict, T: int) -> dict:
+    """Parameters a token's step multiplies by, the bytes a decode step of a batch reads at least (every matrix
+    once, every state read and written, every visible key and value once), and the (query, key) pairs of a
+    prompt of T tokens."""
+    W, V = cfg["width"], cfg["vocab"]
+    active = total = state_bytes = 0
+    seen = []                      # (bytes per visible token, window, kept) of every layer that reads keys
+    pair_flops = 0.0
+    for layer in cfg["layers"]:
+        m, mlp = layer["mixer"], layer["mlp"]
+        if layer["type"] == "attention_2":
+            H, G, D, Vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            mix = W * (2 * H * D + 2 * G * D + G * Vd + H * Vd)
+            w, k = m["mask"]["size"], m["mask"]["keep_first"]
+            seen.append((2 * (2 * G * D + G * Vd), w, k))
+            pairs = sum(min(t + 1, w) + min(k, max(0, t + 1 - w)) for t in range(T))
+            pair_flops += 2 * (2.0 * H * D + 2.0 * H * Vd) * pairs
+        elif layer["type"] == "attention":
+            H, G, D, Vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            mix = W * (H * D + H * Vd) + (0 if m.get("kv_from") is not None else W * (G * D + G * Vd))
+            seen.append((2 * (G * D + G * Vd), 0, 0))
+            pair_flops += (2.0 * H * D + 2.0 * H * Vd) * T * (T + 1) / 2
+        else:
+            l, r = m["left"], m["right"]
+            H, G, D, Vd = l["heads"], l["kv_heads"], l["dim"], l["vdim"]
+            mix = W * (H * D + G * D + G * Vd + H + H * Vd)
+            seen.append((2 * (G * D + G * Vd), 0, 0))
+            pair_flops += (2.0 * H * D + 2.0 * H * Vd) * T * (T + 1) / 2
+            inner, N, R = r["inner"], r["state"], r["dt_rank"]
+            mix += W * 2 * inner + inner * (R + 2 * N) + R * inner + inner * W
+            state_bytes += 2 * 4 * inner * N
+        if mlp["kind"] == "dense":
+            a = t = 2 * W * mlp["ff"]
+        else:
+            r = mlp["router"]
+            a = W * r["experts"] + 3 * W * (mlp["expert"]["ff"] * r["top"] + mlp["shared"]["ff"])
+            t = W * r["experts"] + 3 * W * (mlp["expert"]["ff"] * r["experts"] + mlp["shared"]["ff"])
+        active += mix + a
+        total += mix + t
+
+    def kv_bytes(ctx: float) -> float:
+        return sum(b * (ctx if not w else min(ctx, w) + min(k, max(0.0, ctx - w))) for b, w, k in seen)
+    return dict(layer_params=active, total_params=total, weight_bytes=2 * (total + 2 * V * W), state_bytes=state_bytes,
+                kv_bytes=kv_bytes, pair_flops=pair_flops)
+
+
+def mopitar_comparison(a, pk) -> int:
+    import torch
+    from gguf2bin_b200.api import LLM
+    layers, vocab, batch, T = a.layers or 6, 151936, a.batch or 8, a.prefill_tokens
+    steps, warmup = a.steps or 128, max(a.warmup, 8)
+    max_tokens = batch * (T + warmup + steps + 128)
+    rows = {}
+    clocks = ClockSampler()
+    clocks.start()
+    for name, (width, att, ssm, mls, ff, moe, *_rest) in SOMINEX_SIZES.items():
+        if a.sizes_only and name not in a.sizes_only.split(","):
+            continue
+        row = {}
+        for arch in ("mopitar", "sominex"):
+            if arch == "mopitar":
+                cfg = mopitar_config(width, layers, vocab)
+                sizes = mopitar_bytes_and_flops(cfg, T)
+            else:
+                cfg = sominex_config(width, att, ssm, mls, ff, moe, layers, vocab)
+                sizes = sominex_bytes_and_flops(cfg, T)
+            flops = 2.0 * T * sizes["layer_params"] + sizes["pair_flops"] + 2.0 * vocab * width
+            llm = LLM.random(cfg, seed=0, dtype="bfloat16", max_tokens=max_tokens, max_seqs=batch + 1)
+            first, ms, plain = timed_prompt_step(llm, random_prompts(1, T, vocab, 1), repeats=3)
+            sec, per_step, mean_ctx = decode_device_timed(llm, random_prompts(batch, T, vocab, 100), steps, warmup,
+                                                          vocab, whole_batch_prefill=False)
+            step_bytes = sizes["weight_bytes"] + batch * (sizes["state_bytes"] + sizes["kv_bytes"](mean_ctx))
+            gbs = step_bytes / (sec / steps) / 1e9
+            row[arch] = dict(
+                active_parameters_per_layer_m=round(sizes["layer_params"] / layers / 1e6, 1),
+                prefill_tokens_per_s=round(T / (ms / 1e3)), prefill_ms=round(ms, 3), prefill_plain_ms=round(plain, 3),
+                prefill_frac_of_tensor_peak=round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 3),
+                decode_tokens_per_s=round(batch * steps / sec), decode_ms_per_step=round(sec / steps * 1e3, 4),
+                decode_launches_per_step=per_step, decode_step_mb=round(step_bytes / 1e6, 1), decode_gbs=round(gbs),
+                decode_frac_of_copy_bandwidth=round(gbs / pk["hbm_gbs"], 3))
+            del llm
+            torch.cuda.empty_cache()
+        rows[name] = row
+    print(json.dumps({"metric": "prefill and decode tokens/s of Mopitar beside Sominex at equal sizes (random weights)",
+                      "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+                      "config": {"layers": layers, "vocab": vocab, "prompt_tokens": T, "decode_batch": batch,
+                                 "decode_context_from": T + warmup, "decode_steps": steps, "peaks": pk["source"],
+                                 "l2": "inputs larger than L2 (weights, states and cache read every step)"},
+                      "sizes": rows, "clocks": clocks.stop()}))
+    return 0
+
+
 WORKLOADS = {
     # name: (sizes, batch, what it is)
     "decode": ("0.6b", 8, "every sequence prefilled to half the context, then decoded"),
@@ -582,6 +712,7 @@ WORKLOADS = {
     "senotar": (None, 8, "Senotar beside Qwen3 at equal sizes: a 2,048-token prompt step and batch-8 decode steps each"),
     "levolix": (None, 8, "Levolix beside Qwen3 at equal sizes: a 2,048-token prompt step and batch-8 decode steps each"),
     "sominex": (None, 8, "Sominex beside Qwen3 at equal sizes: a 2,048-token prompt step and batch-8 decode steps each"),
+    "mopitar": (None, 8, "Mopitar beside Sominex at equal sizes: a 2,048-token prompt step and batch-8 decode steps each"),
 }
 
 
@@ -602,7 +733,7 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="length of the prompt of the prefill figure (decode workload; default 2048)")
     ap.add_argument("--sizes-only", default=None,
-                    help="senotar, levolix and sominex workloads: a comma-separated subset of " + ",".join(EQUAL_SIZES))
+                    help="senotar, levolix, sominex and mopitar workloads: a comma-separated subset of " + ",".join(EQUAL_SIZES))
     a = ap.parse_args()
 
     if a.impl == "reference":
@@ -622,6 +753,8 @@ def main() -> int:
         return levolix_comparison(a, peaks())
     if a.workload == "sominex":
         return sominex_comparison(a, peaks())
+    if a.workload == "mopitar":
+        return mopitar_comparison(a, peaks())
 
     import numpy as np
     import torch

@@ -1323,13 +1323,15 @@ extern "C" int g2b_pool_update(const void *cache, void *pooled, int dtype, const
 // ---------------------------------------------------------------------------
 // selective scan: a decay per state entry
 // ---------------------------------------------------------------------------
-// A channel's N state entries are held by L lanes of one warp, P = ceil(N / L) <= MAXP each: lane l
-// holds entries l, l + L, ...  A block owns SEL_THREADS / L channels of one sequence and walks the
-// step's tokens in order, SEL_TILE at a time: a tile's B and C rows, step sizes (softplus applied)
-// and inputs are staged in shared memory by the whole block, then every lane runs its entries
-// through the tile; a channel's read-outs are summed over its lanes by shuffles (an order that
-// depends on N and L only) and leave through shared memory with the skip, the gate and the scale
-// applied.  What a token gets depends on the tokens before it in its sequence only.
+// A channel's N state entries are held by L lanes of one warp, at most P each: lane l holds entries
+// l, l + L, ...  A block owns SEL_THREADS / L channels of one sequence and walks the step's tokens
+// in order, SEL_TILE at a time: a tile's B and C rows, step sizes (softplus applied) and inputs are
+// staged in shared memory by the whole block, then every lane runs its entries through the tile;
+// a channel's read-outs are summed over its lanes by shuffles (an order that depends on N and L
+// only) and leave through shared memory with the skip, the gate and the scale applied.  What a token
+// gets depends on the tokens before it in its sequence only.  The only chain from token to token is
+// one multiply-add per entry; the launcher picks P as small as the step's size allows, so that a
+// prompt of one sequence still fills the GPU with threads (P = 1: a lane an entry).
 #define SEL_THREADS 128
 #define SEL_TILE 16
 
@@ -1364,7 +1366,7 @@ selective_scan_kernel(const T *__restrict__ x, int x_stride, const float *__rest
     const int n = sub + L * i;
     const bool has = live && n < N;
     S[i] = has ? my_state[n] : 0.f;
-    a[i] = has ? A[(size_t)c * N + n] : 0.f;
+    a[i] = has ? A[(size_t)c * N + n] * 1.4426950408889634f : 0.f;     // exp(dt a) = 2^(dt a log2 e)
   }
   for (int t0 = 0; t0 < n_tok; t0 += SEL_TILE) {
     const int here = min(SEL_TILE, n_tok - t0);
@@ -1384,6 +1386,7 @@ selective_scan_kernel(const T *__restrict__ x, int x_stride, const float *__rest
       }
     }
     __syncthreads();
+#pragma unroll 4
     for (int r = 0; r < here; ++r) {                     // lanes beyond the last channel run along on zeros
       const float dt = dts[r * cpb + cl], dx = dt * xs[r * cpb + cl];
       const float *Bs = bcs + (size_t)r * 2 * N, *Cs = Bs + N;
@@ -1392,7 +1395,7 @@ selective_scan_kernel(const T *__restrict__ x, int x_stride, const float *__rest
       for (int i = 0; i < MAXP; ++i) {
         const int n = sub + L * i;
         if (n < N) {
-          S[i] = fmaf(expf(dt * a[i]), S[i], dx * Bs[n]);
+          S[i] = fmaf(exp2f(dt * a[i]), S[i], dx * Bs[n]);
           y = fmaf(S[i], Cs[n], y);
         }
       }
@@ -1427,9 +1430,12 @@ extern "C" int g2b_selective_scan(const void *x, int dtype, int x_stride, const 
   if (N <= 0 || N > 256) G2B_REFUSE("selective_scan: a state of %d entries a channel (1..256)", N);
   const int seqs = seq_meta ? n_seqs : T_tokens;
   if (seqs > 65535) G2B_REFUSE("selective_scan: %d sequences are too many for one launch", seqs);
-  const int maxp = N > 128 ? 8 : 4;
-  int L = 1;
-  while (L * maxp < N) L <<= 1;                           // lanes a channel: 1 .. 32
+  // entries a lane: as few as keep the launch within a few hundred thousand threads (what the GPU holds at
+  // once), and at least what 32 lanes a channel leave; depends on the step's sizes only, never on its data
+  int maxp = N > 128 ? 8 : N > 64 ? 4 : N > 32 ? 2 : 1;
+  auto lanes = [&](int p) { int l = 1; while (l * p < N) l <<= 1; return l; };
+  while (maxp < 8 && (long long)seqs * inner * lanes(maxp) > 300000LL) maxp <<= 1;
+  const int L = lanes(maxp);                             // lanes a channel: 1 .. 32
   const int cpb = SEL_THREADS / L;
   const dim3 grid((inner + cpb - 1) / cpb, seqs);
   const size_t smem = ((size_t)SEL_TILE * 2 * N + 3 * (size_t)SEL_TILE * cpb) * sizeof(float);
@@ -1437,13 +1443,15 @@ extern "C" int g2b_selective_scan(const void *x, int dtype, int x_stride, const 
   g2b_launch(selective_scan_kernel<TYPE, MAXP>, grid, dim3(SEL_THREADS), smem, stream, (const TYPE *)x, x_stride,  \
              dt_raw, dt_stride, dt_bias, (const TYPE *)bc, bc_stride, A, skip, (const TYPE *)z, z_stride, state,   \
              seq_slots, seq_meta, inner, N, L, out_scale, (TYPE *)out, out_stride)
-  if (dtype == G2B_F32) {
-    if (maxp == 4) G2B_SEL(float, 4); else G2B_SEL(float, 8);
-  } else if (dtype == G2B_BF16) {
-    if (maxp == 4) G2B_SEL(bf16, 4); else G2B_SEL(bf16, 8);
-  } else {
-    G2B_REFUSE("selective_scan: unknown dtype %d", dtype);
-  }
+#define G2B_SEL_P(TYPE)                                                                                            \
+  do {                                                                                                             \
+    if (maxp == 1) G2B_SEL(TYPE, 1); else if (maxp == 2) G2B_SEL(TYPE, 2); else if (maxp == 4) G2B_SEL(TYPE, 4);  \
+    else G2B_SEL(TYPE, 8);                                                                                         \
+  } while (0)
+  if (dtype == G2B_F32) G2B_SEL_P(float);
+  else if (dtype == G2B_BF16) G2B_SEL_P(bf16);
+  else G2B_REFUSE("selective_scan: unknown dtype %d", dtype);
+#undef G2B_SEL_P
 #undef G2B_SEL
   return g2b_check_launch("selective_scan");
 }
