@@ -595,15 +595,15 @@ def mopitar_config(width, layers, vocab) -> dict:
         if i % 3 == 0:
             scaling = dict(factor=4.0, original=2048, fast=32.0, slow=1.0)
             out.append(dict(type="attention_2", mlp=mlp,
-                            mixer=dict(heads=H, kv_heads=G, dim=128, vdim=128, scale=128 ** -0.5, diff=0.6,
-                                       mask=dict(size=512, keep_first=4), rot=dict(dims=64, base=1e6, scaling=scaling))))
+                            mixer=dict(heads=H, kv_heads=G, dim=128, vdim=128, scale=128 ** -0.5, diff=0.5,
+                                       mask=dict(size=512, keep_first=8), rot=dict(dims=64, base=1e6, scaling=scaling))))
         elif i % 3 == 1:
-            left = dict(heads=max(H // 2, 1), kv_heads=max(G // 2, 1), dim=128, vdim=128, scale=0.09, softcap=50.0,
+            left = dict(heads=max(H // 2, 1), kv_heads=max(G // 2, 1), dim=128, vdim=128, scale=0.09, softcap=40.0,
                         rot=dict(dims=128, base=5e5))
             right = dict(inner=2 * width, state=16, dt_rank=max(width // 16, 8), conv=4)
-            out.append(dict(type="parallel", mlp=mlp, mixer=dict(left=left, right=right, left_scale=0.8, right_scale=0.5)))
+            out.append(dict(type="parallel", mlp=mlp, mixer=dict(left=left, right=right, left_scale=1.0, right_scale=1.0)))
         else:
-            m = dict(heads=H, kv_heads=G, dim=128, vdim=128, scale=128 ** -0.5, softcap=30.0, rot=dict(dims=128, base=1e4))
+            m = dict(heads=H, kv_heads=G, dim=128, vdim=128, scale=128 ** -0.5, softcap=20.0, rot=dict(dims=128, base=1e4))
             if lender is not None:
                 m["kv_from"] = lender
             else:

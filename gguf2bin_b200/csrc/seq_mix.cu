@@ -1325,38 +1325,50 @@ extern "C" int g2b_pool_update(const void *cache, void *pooled, int dtype, const
 // ---------------------------------------------------------------------------
 // A channel's N state entries are held by L lanes of one warp, at most P each: lane l holds entries
 // l, l + L, ...  A block owns SEL_THREADS / L channels of one sequence and walks the step's tokens
-// in order, SEL_TILE at a time: a tile's B and C rows, step sizes (softplus applied) and inputs are
-// staged in shared memory by the whole block, then every lane runs its entries through the tile;
-// a channel's read-outs are summed over its lanes by shuffles (an order that depends on N and L
-// only) and leave through shared memory with the skip, the gate and the scale applied.  What a token
-// gets depends on the tokens before it in its sequence only.  The only chain from token to token is
-// one multiply-add per entry; the launcher picks P as small as the step's size allows, so that a
-// prompt of one sequence still fills the GPU with threads (P = 1: a lane an entry).
+// in order, SEL_TILE at a time.  The whole block stages a tile in shared memory: (B_n, C_n) pairs, and per
+// channel (dt, dt x) with the softplus applied, and x.  Then every lane runs its entries through the
+// tile: the only chain from token to token is one multiply-add per entry; a lane's share of a read-out
+// goes to shared memory, and after the tile one thread per (token, channel) adds the L shares in lane
+// order (an order that depends on N and L only), adds the skip, applies the gate and the scale and
+// writes the output.  What a token gets depends on the tokens before it in its sequence only.  The
+// launcher picks P as small as the step's size allows, so that a prompt of one sequence still fills
+// the GPU with threads (P = 1: a lane an entry).
 #define SEL_THREADS 128
 #define SEL_TILE 16
 
-template <typename T, int MAXP>
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// `AHEAD`: the next tile's rows are fetched into registers while the current tile is computed (two (token,
+// channel) elements and eight B | C values a thread hold a tile when a channel has 8 to 32 lanes and at most 32
+// entries); otherwise a tile is fetched when its turn comes.
+template <typename T, int MAXP, bool AHEAD>
 __global__ void __launch_bounds__(SEL_THREADS)
 selective_scan_kernel(const T *__restrict__ x, int x_stride, const float *__restrict__ dt_raw, int dt_stride,
                       const float *__restrict__ dt_bias, const T *__restrict__ bc, int bc_stride,
                       const float *__restrict__ A, const float *__restrict__ skip, const T *__restrict__ z,
                       int z_stride, float *__restrict__ state, const int *__restrict__ seq_slots,
-                      const int *__restrict__ seq_meta, int inner, int N, int L, float out_scale,
+                      const int *__restrict__ seq_meta, int inner, int N, int L, int log_cpb, float out_scale,
                       T *__restrict__ out, int out_stride) {
   pdl_launch();
   pdl_wait();
   extern __shared__ float sm[];
-  const int cpb = SEL_THREADS / L;                       // channels of this block
-  float *bcs = sm;                                       // [SEL_TILE][2N]
-  float *dts = bcs + (size_t)SEL_TILE * 2 * N;           // [SEL_TILE][cpb]
-  float *xs = dts + SEL_TILE * cpb;                      // [SEL_TILE][cpb]
-  float *ys = xs + SEL_TILE * cpb;                       // [SEL_TILE][cpb]
+  const int cpb = 1 << log_cpb;                          // channels of this block: its threads / L
+  const int n_threads = blockDim.x, n_warps = blockDim.x >> 5;
+  float2 *bcs = reinterpret_cast<float2 *>(sm);          // [SEL_TILE][N]: (B_n, C_n)
+  float2 *dtx = bcs + (size_t)SEL_TILE * N;              // [SEL_TILE][cpb]: (dt, dt x)
+  float *xs = reinterpret_cast<float *>(dtx + SEL_TILE * cpb);       // [SEL_TILE][cpb]
+  float *part = xs + SEL_TILE * cpb;                     // [SEL_TILE][cpb][L + 1]: the lanes' shares of y
   const int b = blockIdx.y;
   const int first = seq_meta ? seq_meta[4 * b + 0] : b;
   const int n_tok = seq_meta ? seq_meta[4 * b + 1] : 1;
   const int slot = seq_meta ? seq_meta[4 * b + 3] : seq_slots[b];
   const int c0 = blockIdx.x * cpb;
   const int cl = threadIdx.x / L, sub = threadIdx.x % L;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int c = c0 + cl;
   const bool live = c < inner;
   float S[MAXP], a[MAXP];
@@ -1368,47 +1380,121 @@ selective_scan_kernel(const T *__restrict__ x, int x_stride, const float *__rest
     S[i] = has ? my_state[n] : 0.f;
     a[i] = has ? A[(size_t)c * N + n] * 1.4426950408889634f : 0.f;     // exp(dt a) = 2^(dt a log2 e)
   }
+  float *my_part = part + (size_t)cl * (L + 1) + sub;
+  const int part_row = cpb * (L + 1);
+  // AHEAD: element k of a thread is (token r, channel ch) with i = threadIdx.x + k * 128 = r * cpb + (ch - c0), and
+  // B | C value k is row warp + 4 (k / 2), column lane + 32 (k % 2)
+  float f_dt[2], f_x[2], f_z[2], z_now[2], f_bc[8], e_bias[2], e_skip[2];
+  auto fetch = [&](int t0) {
+    const int here = min(SEL_TILE, n_tok - t0);
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int i = threadIdx.x + k * SEL_THREADS, r = i >> log_cpb, ch = c0 + (i & (cpb - 1));
+      f_dt[k] = f_x[k] = f_z[k] = 0.f;
+      if (i < (here << log_cpb) && ch < inner) {
+        const size_t row = (size_t)(first + t0 + r);
+        f_dt[k] = dt_raw[row * dt_stride + ch];
+        f_x[k] = to_f32(x[row * x_stride + ch]);
+        f_z[k] = to_f32(z[row * z_stride + ch]);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int r = warp + 4 * (k >> 1), j = lane + 32 * (k & 1);
+      f_bc[k] = (r < here && j < 2 * N) ? to_f32(bc[(size_t)(first + t0 + r) * bc_stride + j]) : 0.f;
+    }
+  };
+  if (AHEAD) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int ch = c0 + ((threadIdx.x + k * SEL_THREADS) & (cpb - 1));
+      e_bias[k] = ch < inner ? dt_bias[ch] : 0.f;
+      e_skip[k] = ch < inner ? skip[ch] : 0.f;
+    }
+    fetch(0);
+  }
   for (int t0 = 0; t0 < n_tok; t0 += SEL_TILE) {
     const int here = min(SEL_TILE, n_tok - t0);
     __syncthreads();                                     // the tile before has left shared memory
-    for (int i = threadIdx.x; i < here * 2 * N; i += SEL_THREADS) {
-      const int r = i / (2 * N), j = i % (2 * N);
-      bcs[i] = to_f32(bc[(size_t)(first + t0 + r) * bc_stride + j]);
+    if (AHEAD) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int r = warp + 4 * (k >> 1), j = lane + 32 * (k & 1);
+        if (r < here && j < 2 * N)
+          reinterpret_cast<float *>(bcs + (size_t)r * N)[j < N ? 2 * j : 2 * (j - N) + 1] = f_bc[k];
+      }
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int i = threadIdx.x + k * SEL_THREADS;
+        if (i < (here << log_cpb)) {
+          const float dt = softplus_f(f_dt[k] + e_bias[k]);
+          dtx[i] = make_float2(dt, dt * f_x[k]);
+          xs[i] = f_x[k];
+        }
+        z_now[k] = f_z[k];
+      }
+      __syncthreads();
+      if (t0 + SEL_TILE < n_tok) fetch(t0 + SEL_TILE);   // under way while this tile is computed
+    } else {
+      for (int r = warp; r < here; r += n_warps) {                 // a warp a row of B | C
+        const T *row = bc + (size_t)(first + t0 + r) * bc_stride;
+        float *dst = reinterpret_cast<float *>(bcs + (size_t)r * N);
+        for (int j = lane; j < 2 * N; j += 32) dst[j < N ? 2 * j : 2 * (j - N) + 1] = to_f32(row[j]);
+      }
+      for (int i = threadIdx.x; i < (here << log_cpb); i += n_threads) {
+        const int r = i >> log_cpb, ch = c0 + (i & (cpb - 1));
+        float dt = 0.f, xv = 0.f;
+        if (ch < inner) {
+          const size_t row = (size_t)(first + t0 + r);
+          dt = softplus_f(dt_raw[row * dt_stride + ch] + dt_bias[ch]);
+          xv = to_f32(x[row * x_stride + ch]);
+        }
+        dtx[i] = make_float2(dt, dt * xv);
+        xs[i] = xv;
+      }
+      __syncthreads();
     }
-    for (int i = threadIdx.x; i < here * cpb; i += SEL_THREADS) {
-      const int r = i / cpb, ch = c0 + i % cpb;
-      if (ch < inner) {
-        const size_t row = (size_t)(first + t0 + r);
-        dts[i] = softplus_f(dt_raw[row * dt_stride + ch] + dt_bias[ch]);
-        xs[i] = to_f32(x[row * x_stride + ch]);
-      } else {
-        dts[i] = xs[i] = 0.f;
+#pragma unroll
+    for (int r = 0; r < SEL_TILE; ++r) {                 // lanes beyond the last channel run along on zeros
+      if (r < here) {
+        const float2 d = dtx[(r << log_cpb) + cl];
+        float y = 0.f;
+#pragma unroll
+        for (int i = 0; i < MAXP; ++i) {
+          const int n = sub + L * i;
+          if (n < N) {
+            const float2 bcn = bcs[(size_t)r * N + n];
+            S[i] = fmaf(ex2_approx(d.x * a[i]), S[i], d.y * bcn.x);
+            y = fmaf(S[i], bcn.y, y);
+          }
+        }
+        my_part[r * part_row] = y;
       }
     }
     __syncthreads();
-#pragma unroll 4
-    for (int r = 0; r < here; ++r) {                     // lanes beyond the last channel run along on zeros
-      const float dt = dts[r * cpb + cl], dx = dt * xs[r * cpb + cl];
-      const float *Bs = bcs + (size_t)r * 2 * N, *Cs = Bs + N;
-      float y = 0.f;
+    if (AHEAD) {
 #pragma unroll
-      for (int i = 0; i < MAXP; ++i) {
-        const int n = sub + L * i;
-        if (n < N) {
-          S[i] = fmaf(exp2f(dt * a[i]), S[i], dx * Bs[n]);
-          y = fmaf(S[i], Cs[n], y);
+      for (int k = 0; k < 2; ++k) {
+        const int i = threadIdx.x + k * SEL_THREADS, r = i >> log_cpb, ch = c0 + (i & (cpb - 1));
+        if (i < (here << log_cpb) && ch < inner) {
+          const float *p = part + (size_t)i * (L + 1);
+          float y = 0.f;
+          for (int l = 0; l < L; ++l) y += p[l];
+          out[(size_t)(first + t0 + r) * out_stride + ch] =
+              from_f32<T>((y + e_skip[k] * xs[i]) * silu_f(z_now[k]) * out_scale);
         }
       }
-      for (int o = L >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o, 32);
-      if (sub == 0) ys[r * cpb + cl] = y;
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < here * cpb; i += SEL_THREADS) {
-      const int r = i / cpb, ch = c0 + i % cpb;
-      if (ch < inner) {
-        const size_t row = (size_t)(first + t0 + r);
-        const float g = to_f32(z[row * z_stride + ch]);
-        out[row * out_stride + ch] = from_f32<T>((ys[i] + skip[ch] * xs[i]) * silu_f(g) * out_scale);
+    } else {
+      for (int i = threadIdx.x; i < (here << log_cpb); i += n_threads) {
+        const int r = i >> log_cpb, ch = c0 + (i & (cpb - 1));
+        if (ch < inner) {
+          const float *p = part + (size_t)i * (L + 1);
+          float y = 0.f;
+          for (int l = 0; l < L; ++l) y += p[l];
+          const size_t row = (size_t)(first + t0 + r);
+          const float g = to_f32(z[row * z_stride + ch]);
+          out[row * out_stride + ch] = from_f32<T>((y + skip[ch] * xs[i]) * silu_f(g) * out_scale);
+        }
       }
     }
   }
@@ -1436,17 +1522,26 @@ extern "C" int g2b_selective_scan(const void *x, int dtype, int x_stride, const 
   auto lanes = [&](int p) { int l = 1; while (l * p < N) l <<= 1; return l; };
   while (maxp < 8 && (long long)seqs * inner * lanes(maxp) > 300000LL) maxp <<= 1;
   const int L = lanes(maxp);                             // lanes a channel: 1 .. 32
-  const int cpb = SEL_THREADS / L;
+  // 128 threads a block: blocks of 64 and 32 threads stage the same B and C rows for fewer channels and were
+  // slower (2,048 tokens, 4,096 channels of 16 entries: 535 us against 750 and 1,010)
+  const int threads = SEL_THREADS;
+  const int cpb = threads / L;
   const dim3 grid((inner + cpb - 1) / cpb, seqs);
-  const size_t smem = ((size_t)SEL_TILE * 2 * N + 3 * (size_t)SEL_TILE * cpb) * sizeof(float);
-#define G2B_SEL(TYPE, MAXP)                                                                                        \
-  g2b_launch(selective_scan_kernel<TYPE, MAXP>, grid, dim3(SEL_THREADS), smem, stream, (const TYPE *)x, x_stride,  \
-             dt_raw, dt_stride, dt_bias, (const TYPE *)bc, bc_stride, A, skip, (const TYPE *)z, z_stride, state,   \
-             seq_slots, seq_meta, inner, N, L, out_scale, (TYPE *)out, out_stride)
+  int log_cpb = 0;
+  while ((1 << log_cpb) < cpb) ++log_cpb;
+  const size_t smem = ((size_t)SEL_TILE * 2 * N + 3 * (size_t)SEL_TILE * cpb + (size_t)SEL_TILE * cpb * (L + 1)) * sizeof(float);
+  // a tile ahead in registers: prompts only, a (token, channel) tile of at most 256 elements, B | C rows of at most 64
+  const bool ahead = seq_meta && T_tokens > seqs && L >= 8 && N <= 32;
+#define G2B_SEL(TYPE, MAXP, AHEAD)                                                                                 \
+  g2b_launch(selective_scan_kernel<TYPE, MAXP, AHEAD>, grid, dim3(threads), smem, stream, (const TYPE *)x,         \
+             x_stride, dt_raw, dt_stride, dt_bias, (const TYPE *)bc, bc_stride, A, skip, (const TYPE *)z, z_stride, \
+             state, seq_slots, seq_meta, inner, N, L, log_cpb, out_scale, (TYPE *)out, out_stride)
 #define G2B_SEL_P(TYPE)                                                                                            \
   do {                                                                                                             \
-    if (maxp == 1) G2B_SEL(TYPE, 1); else if (maxp == 2) G2B_SEL(TYPE, 2); else if (maxp == 4) G2B_SEL(TYPE, 4);  \
-    else G2B_SEL(TYPE, 8);                                                                                         \
+    if (ahead && maxp == 1) G2B_SEL(TYPE, 1, true); else if (ahead && maxp == 2) G2B_SEL(TYPE, 2, true);           \
+    else if (ahead) G2B_SEL(TYPE, 4, true);                                                                        \
+    else if (maxp == 1) G2B_SEL(TYPE, 1, false); else if (maxp == 2) G2B_SEL(TYPE, 2, false);                      \
+    else if (maxp == 4) G2B_SEL(TYPE, 4, false); else G2B_SEL(TYPE, 8, false);                                     \
   } while (0)
   if (dtype == G2B_F32) G2B_SEL_P(float);
   else if (dtype == G2B_BF16) G2B_SEL_P(bf16);

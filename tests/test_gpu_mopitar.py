@@ -87,7 +87,7 @@ def test_squared_rectifier_feed_forward(ff, width, dtype):
 # ----------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("experts,top,groups,shared", [(6, 2, (3, 2), 16), (8, 3, (2, 1), None), (4, 4, (4, 4), 12),
-                                                      (3, 1, None, None), (16, 2, (4, 3), 24), (12, 4, (6, 2), None)])
+                                                      (3, 1, None, None), (16, 3, (4, 2), 24), (12, 4, (6, 2), None)])
 def test_routed_experts(experts, top, groups, shared, dtype):
     """Choices and weights as the plain router makes them, a row alone and among 76 others."""
     from gguf2bin_b200.config.mopitar import _feed_forward
@@ -146,7 +146,7 @@ def capped_config(H, G, D, V, rot, cap, scale=None):
     (6, 3, 128, 128, 32, 10.0),
     (2, 1, 40, 56, 0, 5.0),          # no rotation
     (5, 5, 8, 8, 4, 0.0),            # no cap
-    (1, 1, 96, 96, 96, 30.0),
+    (1, 1, 80, 80, 80, 25.0),
 ])
 def test_capped_attention_part(H, G, D, V, rot, cap, dtype):
     """Rotation of neighbouring pairs, the score scale, the cap (the queries are large enough for it to
@@ -268,7 +268,7 @@ def test_difference_attention_part(H, G, D, V, window, keep, rot, scaling, dtype
 
 @pytest.mark.parametrize("decode", [False, True])
 @pytest.mark.parametrize("dtype,D", [("float32", 16), ("bfloat16", 64), ("bfloat16", 128)])
-@pytest.mark.parametrize("window,keep", [(20, 3), (64, 5), (70, 66), (9, 1), (40, 0), (130, 129)])
+@pytest.mark.parametrize("window,keep", [(20, 3), (64, 5), (70, 66), (9, 1), (40, 0), (130, 129), (70, 300)])
 def test_window_edges_and_kept_tokens_stand_out(window, keep, decode, dtype, D):
     """Channel 0 of the input feeds nothing but a large value; tokens that carry it sit at the last kept
     position, at the first one that is not kept, and in the middle.  A query sees a flagged token or does
@@ -296,10 +296,10 @@ def test_window_edges_and_kept_tokens_stand_out(window, keep, decode, dtype, D):
         if window + dw < 1 or keep + dk < 0:
             continue
         off = difference_config(2, 1, D, D, window + dw, keep + dk, 8)
-        assert np.abs(MP.difference_mixer(h, off, W, "", EPS) - ref).max() > 2 * allowed, (dw, dk)
+        assert np.abs(MP.difference_mixer(h, off, W, "", EPS) - ref).max() > 1.5 * allowed, (dw, dk)
     part = difference_part(m, W, width, dtype)
     cuts = [[mid + window - 3] + [1] * (n - mid - window + 3)] if decode else [[mid + window - 1, 1, 1, 2]]
-    got = run_part(part, part.cache_need(), [h], cuts, dtype, slots=(4,), pages_per_seq=10)[0]
+    got = run_part(part, part.cache_need(), [h], cuts, dtype, slots=(4,), pages_per_seq=11)[0]
     close(got, ref, dtype, f"window {window} keep {keep}", loose=2.0)
 
 
@@ -313,7 +313,7 @@ def left_part(m, W, width, dtype, scale=1.0):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,G,D,V,rot,cap", [(3, 1, 16, 8, 16, 20.0), (2, 1, 64, 64, 64, 6.0), (6, 2, 48, 64, 48, 3.0),
+@pytest.mark.parametrize("H,G,D,V,rot,cap", [(3, 1, 16, 8, 16, 20.0), (2, 1, 64, 64, 64, 6.0), (6, 2, 40, 64, 40, 3.0),
                                              (2, 2, 8, 12, 4, 2.0), (4, 4, 128, 128, 64, 10.0)])
 def test_gated_unit_attention_part(H, G, D, V, rot, cap, dtype):
     rng = np.random.default_rng(H * 100 + D)
@@ -336,7 +336,7 @@ def ssm_part(m, W, width, dtype, scale=1.0):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("inner,state,rank,taps", [(40, 12, 5, 3), (48, 40, 8, 2), (28, 3, 7, 1), (256, 24, 12, 3),
+@pytest.mark.parametrize("inner,state,rank,taps", [(40, 12, 5, 3), (48, 40, 8, 2), (28, 3, 7, 1), (192, 20, 10, 3),
                                                    (36, 1, 1, 4), (20, 130, 16, 2), (130, 16, 8, 4), (64, 128, 4, 3)])
 def test_selective_scan_part(inner, state, rank, taps, dtype):
     """States of 1 to 130 entries a channel (one to 32 lanes), channel counts that fill no block, 1 to 4
