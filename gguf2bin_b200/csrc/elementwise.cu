@@ -821,10 +821,14 @@ extern "C" int g2b_tanh_norm(const float *x, const float *alpha, const float *w,
   return g2b_check_launch("tanh_norm");
 }
 
-// x += y1 * s1 + y2 * s2 (s: one number per channel; y2 may be absent), all float
+// x += y1 * s1 + y2 * s2 (s: one number per channel; y2 may be absent), all float.  With `alpha`: the new rows
+// once more as tanh(alpha x) * w + b in the compute type, which is what the next layer's norm would compute.
+template <typename TO>
 __global__ void __launch_bounds__(256)
 scaled_join_kernel(float *__restrict__ x, const float *__restrict__ y1, const float *__restrict__ s1,
-                   const float *__restrict__ y2, const float *__restrict__ s2, long long total, int H) {
+                   const float *__restrict__ y2, const float *__restrict__ s2, long long total, int H,
+                   const float *__restrict__ alpha, const float *__restrict__ nw, const float *__restrict__ nb,
+                   TO *__restrict__ normed) {
   pdl_launch();
   pdl_wait();
   if ((H & 3) == 0) {
@@ -841,6 +845,12 @@ scaled_join_kernel(float *__restrict__ x, const float *__restrict__ y1, const fl
     }
     v.x += add.x; v.y += add.y; v.z += add.z; v.w += add.w;
     *reinterpret_cast<float4 *>(x + i) = v;
+    if (alpha) {
+      const float a = alpha[0];
+      const float4 g = *reinterpret_cast<const float4 *>(nw + k), c = *reinterpret_cast<const float4 *>(nb + k);
+      store4(normed + i, fmaf(tanhf(a * v.x), g.x, c.x), fmaf(tanhf(a * v.y), g.y, c.y), fmaf(tanhf(a * v.z), g.z, c.z),
+             fmaf(tanhf(a * v.w), g.w, c.w));
+    }
     return;
   }
   for (int j = 0; j < 4; ++j) {
@@ -849,15 +859,26 @@ scaled_join_kernel(float *__restrict__ x, const float *__restrict__ y1, const fl
     const int k = (int)(i % H);
     float add = y1[i] * s1[k];
     if (y2) add = fmaf(y2[i], s2[k], add);
-    x[i] += add;
+    const float v = x[i] + add;
+    x[i] = v;
+    if (alpha) normed[i] = from_f32<TO>(fmaf(tanhf(alpha[0] * v), nw[k], nb[k]));
   }
 }
 
 extern "C" int g2b_scaled_join(float *x, const float *y1, const float *s1, const float *y2, const float *s2,
-                               int n_rows, int H, cudaStream_t stream) {
+                               int n_rows, int H, const float *alpha, const float *nw, const float *nb, void *normed,
+                               int normed_dtype, cudaStream_t stream) {
   if (n_rows <= 0 || H <= 0) return 0;
   const long long total = (long long)n_rows * H, quads = (total + 3) / 4;
-  g2b_launch(scaled_join_kernel, dim3((unsigned)((quads + 255) / 256)), dim3(256), 0, stream, x, y1, s1, y2, s2, total, H);
+  const dim3 grid((unsigned)((quads + 255) / 256));
+  if (!alpha || normed_dtype == G2B_F32)
+    g2b_launch(scaled_join_kernel<float>, grid, dim3(256), 0, stream, x, y1, s1, y2, s2, total, H, alpha, nw, nb,
+               (float *)normed);
+  else if (normed_dtype == G2B_BF16)
+    g2b_launch(scaled_join_kernel<bf16>, grid, dim3(256), 0, stream, x, y1, s1, y2, s2, total, H, alpha, nw, nb,
+               (bf16 *)normed);
+  else
+    G2B_REFUSE("scaled_join: unknown dtype %d", normed_dtype);
   return g2b_check_launch("scaled_join");
 }
 

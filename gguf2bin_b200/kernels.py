@@ -167,17 +167,27 @@ def tanh_norm(x: torch.Tensor, alpha: torch.Tensor, w: torch.Tensor, b: torch.Te
     _call(f, _ptr(x), _ptr(alpha), _ptr(w), _ptr(b), _ptr(rows), n_rows, H, _ptr(out), _code(out.dtype), _stream())
 
 
-def scaled_join(x32, y1, s1, y2=None, s2=None) -> None:
+def scaled_join(x32, y1, s1, y2=None, s2=None, norm=None, normed_out=None) -> None:
     """x += y1 * s1 (+ y2 * s2): sublayer results [T, H] join the stream, each times one learned number
-    per channel ([H]); everything float32."""
+    per channel ([H]); everything float32.  ``norm`` = (alpha, w, b) with ``normed_out`` [T, H] (compute type):
+    the new rows also leave as tanh(alpha x) * w + b, the next layer's norm, in the same pass."""
     for t, what in ((x32, "stream"), (y1, "result"), (s1, "scale")):
         _need(t, torch.float32, what)
     if y2 is not None:
         _need(y2, torch.float32, "second result")
         _need(s2, torch.float32, "second scale")
-    f = _fn("elementwise.cu", "g2b_scaled_join", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    alpha = w = b = None
+    if norm is not None:
+        alpha, w, b = norm
+        for t, what in ((alpha, "alpha"), (w, "norm weight"), (b, "norm bias")):
+            _need(t, torch.float32, what)
+        if normed_out is None or not normed_out.is_contiguous() or tuple(normed_out.shape) != tuple(x32.shape):
+            raise KernelError("scaled_join: the normed rows need a contiguous output of the stream's shape")
+    f = _fn("elementwise.cu", "g2b_scaled_join", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                                                   c_void_p, c_void_p, c_void_p, c_int, c_void_p])
     _call(f, _ptr(x32), _ptr(y1), _ptr(s1), _ptr(y2), _ptr(s2) if y2 is not None else None, x32.shape[0], x32.shape[1],
-          _stream())
+          _ptr(alpha), _ptr(w), _ptr(b), _ptr(normed_out) if norm is not None else None,
+          _code(normed_out.dtype) if norm is not None else F32, _stream())
 
 
 def relu2(z, out) -> None:

@@ -17,7 +17,7 @@ from ..cache.storage import StateNeed
 from ..config.specs import ConfigError, LayerSpec
 from ..weights.loader import Expected
 from .feed_forward import RoutedExperts
-from .norms import RMSNorm, bind_norm
+from .norms import RMSNorm, TanhNorm, bind_norm
 from .registry import (feed_forward_class, mixer_class, norm_class, register_block)
 
 
@@ -452,7 +452,9 @@ class ParallelScaledBlock:
     stored vectors of the model's width (names ``mixer_scale``, ``ffn_scale``), applied to each sublayer's
     whole result in 32-bit before the two are added and join the stream.  A layer may have no feed-forward.
     Any norm, mixer and feed-forward of the library fit: a sublayer stores into a 32-bit buffer of its own
-    where it can (``forward_store``, ``forward_into``) and adds into a cleared one where it cannot."""
+    where it can (``forward_store``, ``forward_into``) and adds into a cleared one where it cannot.  When the
+    block behind this one is of the same kind with a ``tanh_norm``, the launch that joins the results to the stream
+    also writes that block's normed rows (``StepContext.step_cache`` hands them over)."""
 
     def __init__(self, layer: LayerSpec, hidden_size: int, dtype: torch.dtype, device):
         self.names = dict(layer.block["names"])
@@ -508,8 +510,10 @@ class ParallelScaledBlock:
 
     def forward(self, x32: torch.Tensor, ctx, cache_view) -> None:
         T, H, ws = x32.shape[0], self.hidden, ctx.workspace
-        h = ws.buffer("pscaled.normed", (T, H), self.dtype)
-        self.norm.forward(x32, h)
+        h = ctx.step_cache.pop(("pscaled.normed", x32.data_ptr()), None)
+        if h is None:                              # the block in front left no normed rows
+            h = ws.buffer("pscaled.normed", (T, H), self.dtype)
+            self.norm.forward(x32, h)
         y1 = ws.buffer("pscaled.mixer", (T, H), torch.float32)
         if hasattr(self.mixer, "forward_store"):
             self.mixer.forward_store(h, ctx, cache_view, y1)
@@ -524,7 +528,14 @@ class ParallelScaledBlock:
             else:
                 y2.zero_()
                 ff.forward(h, ctx, y2)
-        kernels.scaled_join(x32, y1, self.mixer_scale, y2, self.ffn_scale)
+        nxt = getattr(ctx, "next_block", None)
+        if isinstance(nxt, ParallelScaledBlock) and isinstance(nxt.norm, TanhNorm) and nxt.norm.weight is not None:
+            # both sublayers have read h by now (stream order): the next block's normed rows take its place
+            n = nxt.norm
+            kernels.scaled_join(x32, y1, self.mixer_scale, y2, self.ffn_scale, norm=(n.alpha, n.weight, n.bias), normed_out=h)
+            ctx.step_cache[("pscaled.normed", x32.data_ptr())] = h
+        else:
+            kernels.scaled_join(x32, y1, self.mixer_scale, y2, self.ffn_scale)
 
 
 register_block("prenorm", PreNormBlock)

@@ -65,6 +65,12 @@ def test_tanh_norm_and_scaled_join(T, H):
     xs = dev(x)
     kernels.scaled_join(xs, dev(y1), dev(s1))
     close(xs.cpu().numpy(), x + y1 * s1, "float32", "scaled join of one")
+    for dtype in ("float32", "bfloat16"):          # the next layer's norm in the same pass
+        xs, out = dev(x), torch.empty((T, H), dtype=DTYPES[dtype], device=DEV)
+        kernels.scaled_join(xs, dev(y1), dev(s1), dev(y2), dev(s2), norm=(dev([alpha]), dev(w), dev(b)), normed_out=out)
+        joined = x + y1 * s1 + y2 * s2
+        close(xs.cpu().numpy(), joined, "float32", "scaled join in front of a norm")
+        close(out.float().cpu().numpy(), np.tanh(alpha * joined) * w + b, dtype, "the norm behind a scaled join", loose=0.5)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
