@@ -157,6 +157,75 @@ proj_norm_rope_cache_kernel(const T *__restrict__ qkv, int row_stride, const flo
   }
 }
 
+// The same prologue where nothing spans the heads (no norm over the whole projection): a warp a (token, head),
+// no block-wide wait.  Heads count through q (nh), then keys (nkv), then values (nvh); every warp stages its head
+// in shared memory, norms it (a weight of one head's size), rotates it, may divide it by its root mean square,
+// and writes it out: q into q_out, keys and values into the token's page, all zero-filled to hd = max(D, V).
+#define HEADWISE_WARPS 8
+template <typename T>
+__global__ void __launch_bounds__(HEADWISE_WARPS * 32)
+proj_rope_cache_headwise_kernel(const T *__restrict__ qkv, int row_stride, const float *__restrict__ bias, int nh,
+                                int nkv, int D, int V, const float *__restrict__ q_w, const float *__restrict__ k_w,
+                                float eps, const float2 *__restrict__ rope, int rot, int interleaved,
+                                const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
+                                const int *__restrict__ page_table, int P, T *__restrict__ cache, int page_size,
+                                T *__restrict__ q_out, float v_norm_eps, int norm_per_head, float unit_eps, int nvh,
+                                long long n_items) {
+  pdl_launch();
+  pdl_wait();
+  extern __shared__ float sm[];                     // a head per warp
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * HEADWISE_WARPS + warp;
+  if (item >= n_items) return;
+  const int heads = nh + nkv + nvh;
+  const int t = (int)(item / heads), h = (int)(item % heads);
+  const int hd = D > V ? D : V;
+  const bool is_v = h >= nh + nkv;
+  const int n = is_v ? V : D;                       // entries of this head
+  const int col = is_v ? (nh + nkv) * D + (h - nh - nkv) * V : h * D;
+  const T *src = qkv + (size_t)t * row_stride + col;
+  float *x = sm + (size_t)warp * hd;
+  for (int d = lane; d < n; d += 32) x[d] = to_f32(src[d]) + (bias ? bias[col + d] : 0.f);
+  __syncwarp();
+  if (!is_v) {
+    const float *w = h < nh ? q_w : k_w;
+    if (norm_per_head && w) {
+      float ss = 0.f;
+      for (int d = lane; d < D; d += 32) ss = fmaf(x[d], x[d], ss);
+      const float inv = 1.f / sqrtf(warp_sum(ss) / (float)D + eps);
+      for (int d = lane; d < D; d += 32) x[d] = x[d] * inv * w[d];
+      __syncwarp();
+    }
+    if (rope) {
+      rotate_in_place(x, rope + (size_t)t * (rot >> 1), rot, interleaved, lane);
+      __syncwarp();
+    }
+    if (unit_eps > 0.f) {
+      float ss = 0.f;
+      for (int d = lane; d < D; d += 32) ss = fmaf(x[d], x[d], ss);
+      const float inv = 1.f / sqrtf(warp_sum(ss) / (float)D + unit_eps);
+      for (int d = lane; d < D; d += 32) x[d] *= inv;
+      __syncwarp();
+    }
+  } else if (v_norm_eps > 0.f) {
+    float ss = 0.f;
+    for (int d = lane; d < V; d += 32) ss = fmaf(x[d], x[d], ss);
+    const float inv = 1.f / sqrtf(warp_sum(ss) / (float)V + v_norm_eps);
+    for (int d = lane; d < V; d += 32) x[d] *= inv;
+    __syncwarp();
+  }
+  T *dst;
+  if (h < nh) {
+    dst = q_out + ((size_t)t * nh + h) * hd;
+  } else {
+    const int pos = tok_pos[t];
+    const size_t page = (size_t)page_table[(size_t)tok_seq[t] * P + pos / page_size];
+    const int plane = is_v ? 1 : 0, kh = is_v ? h - nh - nkv : h - nh;
+    dst = cache + (((page * 2 + plane) * nkv + kh) * page_size + pos % page_size) * hd;
+  }
+  for (int d = lane; d < hd; d += 32) dst[d] = from_f32<T>(d < n ? x[d] : 0.f);
+}
+
 extern "C" int g2b_proj_norm_rope_cache(const void *qkv, int dtype, int row_stride, int T_tokens,
                                         const float *bias, int nh, int nkv, int D, int V, const float *q_w,
                                         const float *k_w, float eps, const float *rope, int rot, int interleaved,
@@ -167,6 +236,27 @@ extern "C" int g2b_proj_norm_rope_cache(const void *qkv, int dtype, int row_stri
   if (rope && (rot <= 0 || rot > D || (rot & 1))) G2B_REFUSE("proj_norm_rope_cache: %d rotated entries of a head of %d", rot, D);
   if (nkv < 0 || nvh < 0 || nvh > nkv) G2B_REFUSE("proj_norm_rope_cache: %d value heads beside %d key heads", nvh, nkv);
   if (nkv > 0 && !cache) G2B_REFUSE("proj_norm_rope_cache: keys without pages to write them to");
+  if (norm_per_head || (!q_w && !k_w)) {                // nothing spans the heads: a warp a (token, head)
+    const int hd = D > V ? D : V;
+    const long long n_items = (long long)T_tokens * (nh + nkv + nvh);
+    const long long blocks = (n_items + HEADWISE_WARPS - 1) / HEADWISE_WARPS;
+    const size_t smem_h = (size_t)HEADWISE_WARPS * hd * sizeof(float);
+    if (blocks <= 0x7fffffffLL && smem_h <= 48 * 1024) {
+      if (dtype == G2B_F32)
+        g2b_launch(proj_rope_cache_headwise_kernel<float>, dim3((unsigned)blocks), dim3(HEADWISE_WARPS * 32), smem_h, stream,
+                   (const float *)qkv, row_stride, bias, nh, nkv, D, V, q_w, k_w, eps, (const float2 *)rope, rot, interleaved,
+                   tok_pos, tok_seq, page_table, P, (float *)cache, page_size, (float *)q_out, v_norm_eps, norm_per_head,
+                   unit_eps, nvh, n_items);
+      else if (dtype == G2B_BF16)
+        g2b_launch(proj_rope_cache_headwise_kernel<bf16>, dim3((unsigned)blocks), dim3(HEADWISE_WARPS * 32), smem_h, stream,
+                   (const bf16 *)qkv, row_stride, bias, nh, nkv, D, V, q_w, k_w, eps, (const float2 *)rope, rot, interleaved,
+                   tok_pos, tok_seq, page_table, P, (bf16 *)cache, page_size, (bf16 *)q_out, v_norm_eps, norm_per_head,
+                   unit_eps, nvh, n_items);
+      else
+        G2B_REFUSE("proj_norm_rope_cache: unknown dtype %d", dtype);
+      return g2b_check_launch("proj_norm_rope_cache");
+    }
+  }
   const size_t smem = ((size_t)(nh + nkv) * D + nkv) * sizeof(float);
   if (smem > 200 * 1024) G2B_REFUSE("proj_norm_rope_cache: q and k of %d entries do not fit a block's shared memory", (nh + nkv) * D);
   if (dtype == G2B_F32) {
