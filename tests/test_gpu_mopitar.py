@@ -153,6 +153,8 @@ def capped_config(H, G, D, V, rot, cap, scale=None):
     (2, 1, 40, 56, 0, 5.0),          # no rotation
     (5, 5, 8, 8, 4, 0.0),            # no cap
     (1, 1, 80, 80, 80, 25.0),
+    (2, 1, 64, 32, 64, 5.0),         # value heads smaller than key heads of a tensor-core size
+    (2, 2, 64, 128, 32, 6.0),        # and larger: keys padded to 128
 ])
 def test_capped_attention_part(H, G, D, V, rot, cap, dtype):
     """Rotation of neighbouring pairs, the score scale, the cap (the queries are large enough for it to
@@ -255,6 +257,8 @@ def difference_config(H, G, D, V, window, keep, rot, scaling=None, diff=0.4):
     (2, 2, 24, 8, 7, None, 24, None),                    # a window alone
     (2, 1, 32, 16, 0, None, 16, None),                   # everything seen
     (1, 1, 12, 20, 33, 40, 0, None),                     # more kept tokens than the window is long; no rotation
+    (2, 1, 128, 64, 40, 2, 64, None),                    # value heads half the size of key heads of 128
+    (4, 2, 32, 64, 24, 5, 16, None),                     # and twice the size, stored at 64
 ])
 def test_difference_attention_part(H, G, D, V, window, keep, rot, scaling, dtype):
     rng = np.random.default_rng(H * 1000 + D + window)
